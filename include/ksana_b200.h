@@ -1,0 +1,142 @@
+/*
+ * ksana_b200 -- C ABI of the B200 (sm_100a) DiT-block kernels.
+ *
+ * KsanaDiT is pure Python: its DiT block reaches its kernels through torch and third-party Python
+ * packages, so it has no FFI of its own.  Each entry point below names the Python call site in
+ * KsanaDiT (path inside that project, file:line) whose work it takes over; the Python classes in
+ * ksanadit_b200/ adapt these to KsanaDiT's operator contracts.
+ *
+ * Conventions
+ *   - every pointer is a device pointer owned by the caller and must stay valid until the work
+ *     queued on `stream` has finished; nothing is allocated or freed here
+ *   - `stream` is a cudaStream_t (NULL = legacy default stream)
+ *   - return value 0 = queued; negative = rejected before any launch
+ *     (-1 invalid argument, -2 CUDA error, -3 unsupported); ksb_last_error() gives the text
+ *   - half-precision tensors carry a dtype tag: KSB_BF16 or KSB_FP16
+ *   - FP8 means e4m3 (finite, max 448); INT8 is signed; scales are fp32
+ */
+#ifndef KSANA_B200_H
+#define KSANA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KSB_BF16 0
+#define KSB_FP16 1
+
+/* GEMM epilogues */
+#define KSB_EPI_NONE 0          /* out = acc*sa*sw + bias */
+#define KSB_EPI_GELU_TANH 1     /* out = gelu_tanh(round(acc*sa*sw + bias)) */
+#define KSB_EPI_GATE_RESIDUAL 2 /* out = resid + round(acc*sa*sw + bias) * gate */
+
+/* token-block sizes of the INT8 scales and padding of the quantised attention operands */
+#define KSB_Q_BLOCK 128
+#define KSB_K_BLOCK 64
+#define KSB_KV_TILE 128
+
+typedef void* ksb_stream_t;
+
+/* Library / error state ------------------------------------------------------------------- */
+int ksb_version(void);
+const char* ksb_last_error(void);
+/* Synchronises the device, returns the status words written by kernels whose bounded waits ran out
+ * (code 0 = none) and clears them. */
+int ksb_device_status(int* code, int* detail);
+int ksb_sm_count(void);
+
+/* Per-token FP8 activation quantiser.
+ * Replaces the eager `(input * (1.0 / scale_input).to(dtype)).to(float8_e4m3fn)` pass of
+ * ksana/operations/linear/fp8_linear.py:52-58, with one scale per row:
+ *   scale[m] = absmax(x[m,:]) / 448 (1.0 for a zero row); q = e4m3(x * half(1/scale[m])).
+ * x: [M,K] half, row stride ldx elements; q: [M,K] e4m3 contiguous; scale: [M]. K % 16 == 0. */
+int ksb_quant_fp8_rowwise(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, void* q, float* scale,
+                          ksb_stream_t stream);
+
+/* The reference's own activation quantisers (fp8_linear.py:48-58): scale_input == NULL ->
+ * clamp(+-448) then cast; else q = e4m3(x * half(1/scale_input[0])) saturated.  scale_out[M] receives
+ * the row scale the GEMM must apply (1 or scale_input[0]). */
+int ksb_quant_fp8_static(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const float* scale_input,
+                         void* q, float* scale_out, ksb_stream_t stream);
+
+/* adaLN modulate fused with the per-token FP8 quantiser.
+ * Replaces `torch.addcmul(shift, LayerNorm(x), 1 + scale)` (ksana/models/wan/wan_model.py:374,391;
+ * ksana/operations/ops.py:41-52) followed by the quantiser above.
+ *   h = shift + LN(x) * (1 + scale), LN without affine, eps; computed in fp32, rounded to half at the
+ *   points the eager path rounds (after LN, after 1+scale, after the addcmul).
+ * shift/scale: [mod_rows, K] half with mod_rows == 1 (broadcast) or M.  h_out (optional, may be NULL)
+ * receives h in half precision.  K % 16 == 0, K <= 16384. */
+int ksb_adaln_quant_fp8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const void* shift,
+                        const void* scale, int64_t mod_rows, float eps, void* h_out, void* q, float* qscale,
+                        ksb_stream_t stream);
+
+/* Affine fp32 LayerNorm fused with the per-token FP8 quantiser (Wan norm3 before cross-attention,
+ * wan_model.py:296-302,390; ops.py:45-50).  w, b: fp32 [K] (b may be NULL). */
+int ksb_layernorm_quant_fp8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const float* w,
+                            const float* b, float eps, void* h_out, void* q, float* qscale, ksb_stream_t stream);
+
+/* FP8 GEMM with per-token x per-output-channel scales on the tcgen05 tensor cores.
+ * Replaces `torch._scaled_mm(input, w, out_dtype, bias, scale_a, scale_b)` of fp8_linear.py:60-63 and,
+ * through the epilogue switch, the eager passes that follow it in the block:
+ * nn.GELU(approximate="tanh") (wan_model.py:317-321) and torch.addcmul(x, y, gate) (wan_model.py:385,392).
+ *   out[m,n] = epi( (sum_k a[m,k]*w[n,k])_fp32 * a_scale[m] * w_scale[n] + bias[n] )
+ * a: [M,K] e4m3 contiguous; w: [N,K] e4m3 contiguous; bias: half [N] or NULL; out: [M,N] half, row
+ * stride ldo.  resid: [M,N] half (row stride ldr) and gate: [gate_rows, N] half with gate_rows 1 or M,
+ * both only for KSB_EPI_GATE_RESIDUAL.  K % 16 == 0, N % 8 == 0. */
+int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const void* bias,
+                 int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo, int epilogue,
+                 const void* resid, int64_t ldr, const void* gate, int64_t gate_rows, ksb_stream_t stream);
+
+/* Gated residual out = x + y * gate (one rounding), for the places where it is not fused into a GEMM
+ * epilogue.  Replaces torch.addcmul(x, y, gate) / x + gate * y (wan_model.py:385,392;
+ * ksana/models/qwen/transformer.py:225-234).  x, y, out: [M,N] half contiguous; gate: [gate_rows, N]. */
+int ksb_gate_residual(const void* x, const void* y, const void* gate, int64_t gate_rows, void* out, int dtype,
+                      int64_t M, int64_t N, ksb_stream_t stream);
+
+/* Sage pre-passes.  The reference reaches them through the un-vendored `sageattention` /
+ * `spas_sage_attn` packages (call sites ksana/operations/attention/backends/sage_attn.py:75-81 and
+ * sage_sla.py:198-228, which shows the pre-pass API: k.mean(-2), per-block INT8 Q/K with fp32 scales,
+ * transposed + padded per-(head, channel) FP8 V).
+ * Input tensors are [L, H, D] views given by element strides (token_stride, head_stride), D == 128
+ * contiguous. */
+
+/* km[h,d] = mean over tokens of k (fp32).  partial: fp32 scratch of ksb_sage_kmean_scratch_floats(L,H,D). */
+int64_t ksb_sage_kmean_scratch_floats(int64_t L, int64_t H, int64_t D);
+int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                   int64_t head_stride, float* partial, float* km, ksb_stream_t stream);
+
+/* INT8 block quantiser: xf = float(x) - mean[h,d] (if mean) then * premul (if premul != 0);
+ * scale[h,b] = absmax(block)/127 (1 if zero); q = clamp(rint(xf/scale), +-127).
+ * out: [H, Lpad, D] int8 with Lpad = roundup(L,128), padding zero-filled; scale: [H, Lpad/block].
+ * block is 128 (Q) or 64 (K). */
+int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                        int64_t head_stride, int block, float premul, const float* mean, void* out,
+                        float* scale, ksb_stream_t stream);
+
+/* V quantiser: vs[h,d] = absmax over tokens / 448 (1 if zero); vt[h,d,l] = e4m3(float(v)/vs), token
+ * axis contiguous and zero-padded to Lpad.  amax: fp32 scratch [H*D] (overwritten). */
+int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                         int64_t head_stride, float* amax, void* vt, float* vs, ksb_stream_t stream);
+
+/* Sage-style attention core: INT8 Q.K^T (s32 accumulate) -> fp32 online softmax in the exp2 domain ->
+ * e4m3 P -> FP8 P.V (f32 accumulate) on tcgen05, dense or block-sparse.
+ * Replaces `sageattn(q, k, v, tensor_layout="NHD")` (sage_attn.py:75-81) and
+ * `block_sparse_sage2_attn_cuda(q, k, v, mask_id=...)` (radial_sage_attn/radial_sage_attn.py:170-176).
+ *   q8 [H,Lq_pad,128], qs [H,Lq_pad/128], k8 [H,Lk_pad,128], ks [H,Lk_pad/64], vt [H,128,Lk_pad], vs [H,128]
+ *   out[l,h,:] (half, element strides out_token_stride / out_head_stride) for l < Lq.
+ * Block-sparse: tile_offsets int32 [Lq_pad/128 + 1] and tile_entries int32 [nnz] (shared by all heads);
+ * entry = kv_tile*4 + keep bits (bit0: tokens 0-63 of the 128-token tile, bit1: tokens 64-127), ascending
+ * kv_tile within a row.  NULL/NULL = dense.  A Q block with an empty list produces zeros.
+ * counter: one int32 of zero-initialised scratch used as the persistent work queue head (NULL = static
+ * round-robin schedule). */
+int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vs,
+                  int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets, const int32_t* tile_entries,
+                  void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride, int32_t* counter,
+                  ksb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KSANA_B200_H */

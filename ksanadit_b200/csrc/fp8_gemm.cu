@@ -1,0 +1,282 @@
+// FP8 (e4m3) GEMM with per-token x per-output-channel scales on the Blackwell tensor cores.
+//
+//   out[m,n] = epi( (sum_k A[m,k] * W[n,k])_f32 * sa[m] * sw[n] + bias[n] )
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: 128 x 128 B tile of A and 256 x 128 B tile of W per stage, 128-byte swizzle,
+//               STAGES-deep ring in shared memory, completion on mbarriers
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (kind::f8f6f4, M128 N256 K32) from shared-memory
+//               descriptors into a tensor-memory accumulator; two accumulators (2 x 256 columns) alternate
+//               so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one row per thread), apply scales / bias / fused
+//               GELU-tanh or gated residual, convert to half, store
+// Tiles are visited in groups of GROUP_M row-tiles so that CTAs running at the same time share operand
+// tiles in L2.  Ragged M, N, K edges rely on TMA zero fill for loads and on predicated stores.
+//
+// Tensor-bound: 2*M*N*K flop per launch; minimal traffic M*K + N*K + 2*M*N bytes.
+#include "../../include/ksana_b200.h"
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace ksb {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 128;  // BK in bytes == e4m3 elements
+constexpr int UMMA_K = 32;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 8;
+constexpr int TMEM_COLS = 512;
+constexpr int KERNEL_ID = 1;
+// dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers]
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256;
+
+struct Params {
+  int M, N, K;
+  const float* sa;
+  const float* sw;
+  const void* bias;
+  void* out;
+  int64_t ldo;
+  int epilogue;
+  const void* resid;
+  int64_t ldr;
+  const void* gate;
+  int64_t gate_rows;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  // 0.5 x (1 + tanh(u)) = x * sigmoid(2u),  u = sqrt(2/pi) (x + 0.044715 x^3)
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return x / (1.f + __expf(-2.f * u));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  float* colp = reinterpret_cast<float*>(gen + STAGES * STAGE_BYTES);  // [sw | bias | gate] x BN
+  const uint32_t bars = base + STAGES * STAGE_BYTES + 3 * BN * 4;
+  const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
+  const uint32_t tmem_slot = tempty0 + 16;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + STAGES * STAGE_BYTES + 3 * BN * 4 + 16 * STAGES + 32);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_k = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_w);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        for (int k = 0; k < num_k; ++k, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, p.status, (KERNEL_ID << 16) | 1)) { ok = false; break; }
+          const uint32_t sa = base + s * STAGE_BYTES;
+          mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, full0 + 8 * s, k * BK, tm * BM);
+          tma_load_2d(sa + A_BYTES, &tmap_w, full0 + 8 * s, k * BK, tn * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = IDESC_F8_E4M3_F32(BM, BN);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!mbar_wait(tempty0 + 8 * acc, aph ^ 1, p.status, (KERNEL_ID << 16) | 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int k = 0; k < num_k; ++k, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(full0 + 8 * s, ph, p.status, (KERNEL_ID << 16) | 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * STAGE_BYTES;
+          const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            mma_f8_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0);
+          mma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+        }
+        if (ok) mma_commit(tfull0 + 8 * acc);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int et = threadIdx.x - 64;
+    uint32_t tcount = 0;
+    bool failed = false;
+    T* out = static_cast<T*>(p.out);
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      // All four epilogue warps leave together if any of their waits ran out (a warp must never be
+      // left alone at the named barrier below); the same barrier protects the reuse of colp.
+      if (named_bar_or(1, 128, failed)) break;
+      // stage the per-column parameters of this tile
+      for (int c = et; c < BN; c += 128) {
+        const int n = tn * BN + c;
+        const bool in = n < p.N;
+        colp[c] = in ? p.sw[n] : 0.f;
+        colp[BN + c] = (in && p.bias) ? HalfOps<T>::to_f(static_cast<const T*>(p.bias)[n]) : 0.f;
+        colp[2 * BN + c] = (in && p.gate && p.gate_rows == 1) ? HalfOps<T>::to_f(static_cast<const T*>(p.gate)[n]) : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait_warp(tfull0 + 8 * acc, aph, p.status, (KERNEL_ID << 16) | 4)) { failed = true; continue; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sa = row_ok ? p.sa[row] : 0.f;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      T* orow = out + static_cast<int64_t>(row) * p.ldo + tn * BN;
+      const T* rrow = p.resid ? static_cast<const T*>(p.resid) + static_cast<int64_t>(row) * p.ldr + tn * BN : nullptr;
+      const T* grow = (p.gate && p.gate_rows != 1) ? static_cast<const T*>(p.gate) + static_cast<int64_t>(row) * p.N + tn * BN : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c0, r);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            const int cb = c0 + v8 * 8;
+            if (tn * BN + cb < p.N) {
+              float y[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float a = __uint_as_float(r[v8 * 8 + i]);
+                y[i] = a * sa * colp[cb + i] + colp[BN + cb + i];
+              }
+              if (p.epilogue == KSB_EPI_GELU_TANH) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = gelu_tanh(HalfOps<T>::to_f(HalfOps<T>::from_f(y[i])));
+              } else if (p.epilogue == KSB_EPI_GATE_RESIDUAL) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + cb);
+                const T* rt = reinterpret_cast<const T*>(&rv);
+                uint4 gv = make_uint4(0, 0, 0, 0);
+                if (grow) gv = *reinterpret_cast<const uint4*>(grow + cb);
+                const T* gt = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float g = grow ? HalfOps<T>::to_f(gt[i]) : colp[2 * BN + cb + i];
+                  y[i] = fmaf(HalfOps<T>::to_f(HalfOps<T>::from_f(y[i])), g, HalfOps<T>::to_f(rt[i]));
+                }
+              }
+              uint4 o;
+              T* ot = reinterpret_cast<T*>(&o);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) ot[i] = HalfOps<T>::from_f(y[i]);
+              *reinterpret_cast<uint4*>(orow + cb) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+    }
+  }
+
+  // ------------------------------------------------------------------ common exit
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm
+}  // namespace ksb
+
+using namespace ksb;
+
+extern "C" int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                            const void* bias, int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo,
+                            int epilogue, const void* resid, int64_t ldr, const void* gate, int64_t gate_rows,
+                            ksb_stream_t stream) {
+  if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
+  if (M < 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return fail(KSB_ERR_INVALID, "bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (K % 16 != 0 || N % 8 != 0) return fail(KSB_ERR_INVALID, "K must be a multiple of 16 and N of 8 (K=%lld N=%lld)", (long long)K, (long long)N);
+  if (M == 0) return 0;
+  if (!a || !a_scale || !w || !w_scale || !out) return fail(KSB_ERR_INVALID, "null pointer");
+  if (ldo < N || ldo % 8 != 0 || !aligned16(out)) return fail(KSB_ERR_INVALID, "out must be 16-byte aligned with ldo >= N, ldo %% 8 == 0");
+  if (epilogue < KSB_EPI_NONE || epilogue > KSB_EPI_GATE_RESIDUAL) return fail(KSB_ERR_INVALID, "unknown epilogue %d", epilogue);
+  if (epilogue == KSB_EPI_GATE_RESIDUAL) {
+    if (!resid || !gate) return fail(KSB_ERR_INVALID, "gate-residual epilogue needs resid and gate");
+    if (ldr < N || ldr % 8 != 0 || !aligned16(resid) || !aligned16(gate)) return fail(KSB_ERR_INVALID, "resid/gate alignment");
+    if (gate_rows != 1 && gate_rows != M) return fail(KSB_ERR_INVALID, "gate_rows must be 1 or M");
+  } else {
+    resid = nullptr;
+    gate = nullptr;
+  }
+  CUtensorMap ta, tw;
+  if (int rc = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K, (uint64_t)M, (uint64_t)K, gemm::BK, gemm::BM)) return rc;
+  if (int rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, (uint64_t)K, (uint64_t)N, (uint64_t)K, gemm::BK, gemm::BN)) return rc;
+  gemm::Params p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = out; p.ldo = ldo; p.epilogue = epilogue;
+  p.resid = resid; p.ldr = ldr; p.gate = gate; p.gate_rows = gate_rows;
+  p.status = status_words();
+  if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");
+  const int tiles = (int)((M + gemm::BM - 1) / gemm::BM) * (int)((N + gemm::BN - 1) / gemm::BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == KSB_BF16) {
+    if (cudaFuncSetAttribute(gemm::fp8_gemm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES) != cudaSuccess)
+      return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
+    gemm::fp8_gemm_kernel<__nv_bfloat16><<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(ta, tw, p);
+  } else {
+    if (cudaFuncSetAttribute(gemm::fp8_gemm_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES) != cudaSuccess)
+      return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
+    gemm::fp8_gemm_kernel<__half><<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(ta, tw, p);
+  }
+  return check_launch("fp8 gemm");
+}

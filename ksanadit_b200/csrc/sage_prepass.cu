@@ -1,0 +1,252 @@
+// HBM-bound pre-passes of the Sage-style attention: K token-mean (smoothing vector), per-block INT8
+// quantisation of Q and K, per-(head, channel) FP8 quantisation of V with the token axis made
+// contiguous.  Inputs are [L, H, 128] half tensors addressed by element strides, so they can be views
+// into a fused QKV projection output.
+//
+// Algorithmic bytes per token and head (D = 128): Q or K quantiser 256 read + 128 written;
+// K mean 256 read; V quantiser 2 x 256 read + 128 written.
+#include "../../include/ksana_b200.h"
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace ksb {
+namespace prep {
+
+constexpr int D = 128;
+constexpr int THREADS = 256;
+constexpr int MEAN_CHUNK = 512;  // tokens per CTA in the mean / amax passes
+
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const T* t = reinterpret_cast<const T*>(&a);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = HalfOps<T>::to_f(t[i]);
+}
+
+// ---------------------------------------------------------------------------------- K mean / V amax
+// grid (chunks, H).  256 threads = 16 token lanes x 16 column groups of 8 channels.
+template <typename T, bool IS_MAX>
+__global__ void __launch_bounds__(THREADS) column_reduce_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs,
+                                                                 float* __restrict__ out, int H) {
+  __shared__ float red[16][D + 1];
+  const int h = blockIdx.y, chunk = blockIdx.x;
+  const int tl = threadIdx.x >> 4, cg = threadIdx.x & 15;
+  const int64_t l0 = (int64_t)chunk * MEAN_CHUNK;
+  const int64_t l1 = min(L, l0 + MEAN_CHUNK);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int64_t l = l0 + tl; l < l1; l += 16) {
+    float f[8];
+    load8<T>(x + l * ts + (int64_t)h * hs + cg * 8, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = IS_MAX ? fmaxf(acc[i], fabsf(f[i])) : acc[i] + f[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[tl][cg * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float r = red[0][threadIdx.x];
+#pragma unroll
+    for (int j = 1; j < 16; ++j) r = IS_MAX ? fmaxf(r, red[j][threadIdx.x]) : r + red[j][threadIdx.x];
+    if (IS_MAX) {
+      // non-negative floats order like their bit patterns
+      atomicMax(reinterpret_cast<int*>(out) + h * D + threadIdx.x, __float_as_int(r));
+    } else {
+      out[((int64_t)chunk * H + h) * D + threadIdx.x] = r;  // partial sums [chunk][h][d]
+    }
+  }
+}
+
+__global__ void mean_finish_kernel(const float* __restrict__ partial, int chunks, int HD, float inv_L, float* __restrict__ km) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= HD) return;
+  float s = 0.f;
+  for (int c = 0; c < chunks; ++c) s += partial[(int64_t)c * HD + i];
+  km[i] = s * inv_L;
+}
+
+// ---------------------------------------------------------------------------------- INT8 block quantiser
+// grid (Lpad / BLOCK, H).  A block of BLOCK tokens x 128 channels lives in registers between the
+// absmax reduction and the quantisation.
+template <typename T, int BLOCK>
+__global__ void __launch_bounds__(THREADS) int8_block_quant_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs,
+                                                                    float premul, const float* __restrict__ mean,
+                                                                    int8_t* __restrict__ out, float* __restrict__ scale,
+                                                                    int64_t Lpad) {
+  constexpr int VEC = BLOCK * D / 8 / THREADS;  // 16-byte vectors per thread (8 for 128 tokens, 4 for 64)
+  __shared__ float red[THREADS / 32];
+  const int h = blockIdx.y, b = blockIdx.x;
+  const int64_t l0 = (int64_t)b * BLOCK;
+  float v[VEC][8];
+  float am = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int j = threadIdx.x + i * THREADS;
+    const int r = j >> 4, c = (j & 15) * 8;
+    const int64_t l = l0 + r;
+    if (l < L) {
+      load8<T>(x + l * ts + (int64_t)h * hs + c, v[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float f = v[i][e];
+        if (mean) f = f - mean[h * D + c + e];
+        if (premul != 0.f) f = f * premul;
+        v[i][e] = f;
+        am = fmaxf(am, fabsf(f));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+    }
+  }
+  am = warp_max(am);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = am;
+  __syncthreads();
+  am = red[0];
+#pragma unroll
+  for (int i = 1; i < THREADS / 32; ++i) am = fmaxf(am, red[i]);
+  const float sc = (am > 0.f) ? __fdiv_rn(am, 127.f) : 1.f;
+  if (threadIdx.x == 0) scale[(int64_t)h * (Lpad / BLOCK) + b] = sc;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int j = threadIdx.x + i * THREADS;
+    const int r = j >> 4, c = (j & 15) * 8;
+    uint32_t w[2] = {0, 0};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int q = __float2int_rn(__fdiv_rn(v[i][e], sc));
+      q = max(-127, min(127, q));
+      w[e >> 2] |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e & 3));
+    }
+    *reinterpret_cast<uint2*>(out + ((int64_t)h * Lpad + l0 + r) * D + c) = make_uint2(w[0], w[1]);
+  }
+}
+
+// ---------------------------------------------------------------------------------- V quantiser + transpose
+// grid (Lpad / 128, H): tile of 128 tokens x 128 channels -> vt[h][d][l0 .. l0+127] e4m3.
+template <typename T>
+__global__ void __launch_bounds__(THREADS) v_quant_transpose_kernel(const T* __restrict__ v, int64_t L, int64_t ts, int64_t hs,
+                                                                     const float* __restrict__ amax, uint8_t* __restrict__ vt,
+                                                                     float* __restrict__ vs, int64_t Lpad) {
+  __shared__ __align__(16) uint8_t tile[D][128 + 16];  // [d][token], padded rows
+  __shared__ float s_sc[D];
+  const int h = blockIdx.y;
+  const int64_t l0 = (int64_t)blockIdx.x * 128;
+  if (threadIdx.x < D) {
+    const float a = amax[h * D + threadIdx.x];
+    const float sc = (a > 0.f) ? __fdiv_rn(a, 448.f) : 1.f;
+    s_sc[threadIdx.x] = sc;
+    if (blockIdx.x == 0) vs[h * D + threadIdx.x] = sc;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int j = threadIdx.x + i * THREADS;
+    const int r = j >> 4, c = (j & 15) * 8;
+    const int64_t l = l0 + r;
+    float f[8];
+    if (l < L) {
+      load8<T>(v + l * ts + (int64_t)h * hs + c, f);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const uint16_t pr = cvt_e4m3x2(__fdiv_rn(f[e], s_sc[c + e]), __fdiv_rn(f[e + 1], s_sc[c + e + 1]));
+      tile[c + e][r] = static_cast<uint8_t>(pr & 0xff);
+      tile[c + e + 1][r] = static_cast<uint8_t>(pr >> 8);
+    }
+  }
+  __syncthreads();
+  // 128 rows (d) x 128 bytes: 8 x 16-byte stores per row
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int j = threadIdx.x + i * THREADS;
+    const int d = j >> 3, c = (j & 7) * 16;
+    const uint4 val = *reinterpret_cast<const uint4*>(&tile[d][c]);
+    *reinterpret_cast<uint4*>(vt + ((int64_t)h * D + d) * Lpad + l0 + c) = val;
+  }
+}
+
+int validate(const void* x, int dtype, int64_t L, int64_t H, int64_t Dh, int64_t ts, int64_t hs) {
+  if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
+  if (Dh != D) return fail(KSB_ERR_UNSUPPORTED, "head size %lld is not supported (only 128)", (long long)Dh);
+  if (L <= 0 || H <= 0 || H > 65535) return fail(KSB_ERR_INVALID, "bad shape L=%lld H=%lld", (long long)L, (long long)H);
+  if (!x || !aligned16(x) || ts % 8 != 0 || hs % 8 != 0) return fail(KSB_ERR_INVALID, "input must be 16-byte aligned with strides multiple of 8 elements");
+  return 0;
+}
+
+inline int64_t pad128(int64_t L) { return (L + 127) / 128 * 128; }
+
+}  // namespace prep
+}  // namespace ksb
+
+using namespace ksb;
+
+extern "C" {
+
+int64_t ksb_sage_kmean_scratch_floats(int64_t L, int64_t H, int64_t D) {
+  return ((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK) * H * D;
+}
+
+int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,
+                   float* partial, float* km, ksb_stream_t stream) {
+  if (int rc = prep::validate(k, dtype, L, H, D, token_stride, head_stride)) return rc;
+  if (!partial || !km) return fail(KSB_ERR_INVALID, "null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int chunks = (int)((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK);
+  dim3 grid(chunks, (unsigned)H);
+  if (dtype == KSB_BF16)
+    prep::column_reduce_kernel<__nv_bfloat16, false><<<grid, prep::THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(k), L, token_stride, head_stride, partial, (int)H);
+  else
+    prep::column_reduce_kernel<__half, false><<<grid, prep::THREADS, 0, st>>>(static_cast<const __half*>(k), L, token_stride, head_stride, partial, (int)H);
+  if (int rc = check_launch("k mean (partial)")) return rc;
+  const int HD = (int)(H * D);
+  prep::mean_finish_kernel<<<(HD + 255) / 256, 256, 0, st>>>(partial, chunks, HD, 1.0f / (float)L, km);
+  return check_launch("k mean (finish)");
+}
+
+int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,
+                        int block, float premul, const float* mean, void* out, float* scale, ksb_stream_t stream) {
+  if (int rc = prep::validate(x, dtype, L, H, D, token_stride, head_stride)) return rc;
+  if (block != 128 && block != 64) return fail(KSB_ERR_INVALID, "block must be 128 or 64");
+  if (!out || !scale || !aligned16(out)) return fail(KSB_ERR_INVALID, "null or unaligned output");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t Lpad = prep::pad128(L);
+  dim3 grid((unsigned)(Lpad / block), (unsigned)H);
+  int8_t* o = static_cast<int8_t*>(out);
+#define KSB_LAUNCH_Q(T, B) prep::int8_block_quant_kernel<T, B><<<grid, prep::THREADS, 0, st>>>(static_cast<const T*>(x), L, token_stride, head_stride, premul, mean, o, scale, Lpad)
+  if (dtype == KSB_BF16) {
+    if (block == 128) KSB_LAUNCH_Q(__nv_bfloat16, 128); else KSB_LAUNCH_Q(__nv_bfloat16, 64);
+  } else {
+    if (block == 128) KSB_LAUNCH_Q(__half, 128); else KSB_LAUNCH_Q(__half, 64);
+  }
+#undef KSB_LAUNCH_Q
+  return check_launch("int8 block quantiser");
+}
+
+int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,
+                         float* amax, void* vt, float* vs, ksb_stream_t stream) {
+  if (int rc = prep::validate(v, dtype, L, H, D, token_stride, head_stride)) return rc;
+  if (!amax || !vt || !vs || !aligned16(vt)) return fail(KSB_ERR_INVALID, "null or unaligned output");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(amax, 0, sizeof(float) * H * D, st) != cudaSuccess) return fail(KSB_ERR_CUDA, "memset failed");
+  const int chunks = (int)((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK);
+  dim3 g1(chunks, (unsigned)H);
+  const int64_t Lpad = prep::pad128(L);
+  dim3 g2((unsigned)(Lpad / 128), (unsigned)H);
+  if (dtype == KSB_BF16) {
+    prep::column_reduce_kernel<__nv_bfloat16, true><<<g1, prep::THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(v), L, token_stride, head_stride, amax, (int)H);
+    if (int rc = check_launch("v absmax")) return rc;
+    prep::v_quant_transpose_kernel<__nv_bfloat16><<<g2, prep::THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(v), L, token_stride, head_stride, amax, static_cast<uint8_t*>(vt), vs, Lpad);
+  } else {
+    prep::column_reduce_kernel<__half, true><<<g1, prep::THREADS, 0, st>>>(static_cast<const __half*>(v), L, token_stride, head_stride, amax, (int)H);
+    if (int rc = check_launch("v absmax")) return rc;
+    prep::v_quant_transpose_kernel<__half><<<g2, prep::THREADS, 0, st>>>(static_cast<const __half*>(v), L, token_stride, head_stride, amax, static_cast<uint8_t*>(vt), vs, Lpad);
+  }
+  return check_launch("v quantiser");
+}
+
+}  // extern "C"

@@ -1,0 +1,203 @@
+"""Functional wrappers: torch CUDA tensors in, torch CUDA tensors out, every kernel through the C ABI.
+
+torch is used for device memory and streams only.  Nothing here computes on the CPU or falls back to
+a PyTorch implementation.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+Q_BLOCK, K_BLOCK, KV_TILE = 128, 64, 128
+LOG2E = 1.4426950408889634
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.BF16
+    if t.dtype == torch.float16:
+        return _lib.FP16
+    raise TypeError(f"expected bfloat16 or float16, got {t.dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.KsanaB200Error("ksanadit_b200 kernels need CUDA tensors (no CPU path exists)")
+
+
+def pad128(n: int) -> int:
+    return (n + 127) // 128 * 128
+
+
+# ----------------------------------------------------------------------------- FP8 Linear pieces
+
+
+def quant_fp8_rowwise(x: torch.Tensor):
+    """x [M,K] half (row stride allowed) -> (q [M,K] float8_e4m3fn, scale [M] fp32)."""
+    _cuda(x)
+    assert x.dim() == 2 and x.stride(1) == 1
+    M, K = x.shape
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().ksb_quant_fp8_rowwise(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(q), _p(s), _stream()),
+               "ksb_quant_fp8_rowwise")
+    return q, s
+
+
+def quant_fp8_static(x: torch.Tensor, scale_input: torch.Tensor | None):
+    _cuda(x, scale_input)
+    assert x.dim() == 2 and x.stride(1) == 1
+    M, K = x.shape
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().ksb_quant_fp8_static(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(scale_input), _p(q), _p(s),
+                                                _stream()), "ksb_quant_fp8_static")
+    return q, s
+
+
+def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False):
+    """h = shift + LN(x)*(1+scale) -> per-token FP8.  x [M,K]; shift/scale [1,K] or [M,K]."""
+    _cuda(x, shift, scale)
+    M, K = x.shape
+    shift = shift.reshape(-1, K).contiguous()
+    scale = scale.reshape(-1, K).contiguous()
+    assert shift.shape == scale.shape and shift.dtype == x.dtype == scale.dtype
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    h = torch.empty(M, K, dtype=x.dtype, device=x.device) if want_h else None
+    _lib.check(_lib.load().ksb_adaln_quant_fp8(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(shift), _p(scale),
+                                               shift.shape[0], float(eps), _p(h), _p(q), _p(s), _stream()),
+               "ksb_adaln_quant_fp8")
+    return (q, s, h) if want_h else (q, s)
+
+
+def layernorm_quant_fp8(x, w, b, eps=1e-6, want_h=False):
+    _cuda(x, w, b)
+    M, K = x.shape
+    w = w.float().contiguous()
+    b = None if b is None else b.float().contiguous()
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    h = torch.empty(M, K, dtype=x.dtype, device=x.device) if want_h else None
+    _lib.check(_lib.load().ksb_layernorm_quant_fp8(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(w), _p(b), float(eps),
+                                                   _p(h), _p(q), _p(s), _stream()), "ksb_layernorm_quant_fp8")
+    return (q, s, h) if want_h else (q, s)
+
+
+def fp8_gemm(a_q, a_scale, w_q, w_scale, bias=None, out_dtype=torch.bfloat16, epilogue=_lib.EPI_NONE, resid=None, gate=None,
+             out=None):
+    """out[M,N] = epi((a_q @ w_q.T) * a_scale[:,None] * w_scale[None,:] + bias)."""
+    _cuda(a_q, a_scale, w_q, w_scale, bias, resid, gate, out)
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    assert w_q.shape[1] == K and a_q.is_contiguous() and w_q.is_contiguous()
+    assert a_scale.dtype == torch.float32 and w_scale.dtype == torch.float32 and a_scale.numel() == M and w_scale.numel() == N
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    dt = _lib.BF16 if out.dtype == torch.bfloat16 else _lib.FP16
+    if bias is not None:
+        bias = bias.to(out.dtype).contiguous()
+    ldr, gate_rows = 0, 0
+    if epilogue == _lib.EPI_GATE_RESIDUAL:
+        assert resid is not None and gate is not None and resid.dtype == out.dtype
+        gate = gate.reshape(-1, N).to(out.dtype).contiguous()
+        gate_rows = gate.shape[0]
+        ldr = resid.stride(0) if M > 1 else N
+    _lib.check(_lib.load().ksb_fp8_gemm(_p(a_q), _p(a_scale), _p(w_q), _p(w_scale), _p(bias), M, N, K, _p(out), dt,
+                                        out.stride(0) if M > 1 else N, epilogue, _p(resid), ldr, _p(gate), gate_rows, _stream()),
+               "ksb_fp8_gemm")
+    return out
+
+
+def gate_residual(x, y, gate):
+    _cuda(x, y, gate)
+    M, N = x.shape
+    gate = gate.reshape(-1, N).to(x.dtype).contiguous()
+    out = torch.empty_like(x)
+    _lib.check(_lib.load().ksb_gate_residual(_p(x.contiguous()), _p(y.contiguous()), _p(gate), gate.shape[0], _p(out), _dt(x), M, N,
+                                             _stream()), "ksb_gate_residual")
+    return out
+
+
+# ----------------------------------------------------------------------------- Sage attention pieces
+
+
+def _lhd(x):
+    """[L,H,D] view with D contiguous -> (L,H,D, token_stride, head_stride)."""
+    assert x.dim() == 3 and x.stride(2) == 1
+    return x.shape[0], x.shape[1], x.shape[2], x.stride(0), x.stride(1)
+
+
+def sage_kmean(k):
+    _cuda(k)
+    L, H, D, ts, hs = _lhd(k)
+    lib = _lib.load()
+    partial = torch.empty(lib.ksb_sage_kmean_scratch_floats(L, H, D), dtype=torch.float32, device=k.device)
+    km = torch.empty(H, D, dtype=torch.float32, device=k.device)
+    _lib.check(lib.ksb_sage_kmean(_p(k), _dt(k), L, H, D, ts, hs, _p(partial), _p(km), _stream()), "ksb_sage_kmean")
+    return km
+
+
+def sage_quant_int8(x, block, premul=0.0, mean=None):
+    """x [L,H,128] -> (int8 [H,Lpad,128], scale [H, Lpad/block])."""
+    _cuda(x, mean)
+    L, H, D, ts, hs = _lhd(x)
+    Lp = pad128(L)
+    out = torch.empty(H, Lp, D, dtype=torch.int8, device=x.device)
+    sc = torch.empty(H, Lp // block, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().ksb_sage_quant_int8(_p(x), _dt(x), L, H, D, ts, hs, block, float(premul), _p(mean), _p(out), _p(sc),
+                                               _stream()), "ksb_sage_quant_int8")
+    return out, sc
+
+
+def sage_quant_v(v):
+    """v [L,H,128] -> (vt [H,128,Lpad] float8_e4m3fn, vs [H,128])."""
+    _cuda(v)
+    L, H, D, ts, hs = _lhd(v)
+    Lp = pad128(L)
+    amax = torch.empty(H * D, dtype=torch.float32, device=v.device)
+    vt = torch.empty(H, D, Lp, dtype=torch.float8_e4m3fn, device=v.device)
+    vs = torch.empty(H, D, dtype=torch.float32, device=v.device)
+    _lib.check(_lib.load().ksb_sage_quant_v_fp8(_p(v), _dt(v), L, H, D, ts, hs, _p(amax), _p(vt), _p(vs), _stream()),
+               "ksb_sage_quant_v_fp8")
+    return vt, vs
+
+
+def q_premul(head_dim: int, sm_scale: float | None = None) -> float:
+    sc = head_dim ** -0.5 if sm_scale is None else sm_scale
+    return float(torch.tensor(sc * LOG2E, dtype=torch.float64).to(torch.float32))
+
+
+def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, tile_offsets=None, tile_entries=None, out=None):
+    """Quantised operands -> out [Lq, H, 128]."""
+    _cuda(q8, qs, k8, ks, vt, vs, tile_offsets, tile_entries, out)
+    H = q8.shape[0]
+    if out is None:
+        out = torch.empty(Lq, H, 128, dtype=out_dtype, device=q8.device)
+    assert out.stride(2) == 1
+    dt = _lib.BF16 if out.dtype == torch.bfloat16 else _lib.FP16
+    _lib.check(_lib.load().ksb_sage_attn(_p(q8), _p(qs), _p(k8), _p(ks), _p(vt), _p(vs), H, Lq, Lk, _p(tile_offsets),
+                                         _p(tile_entries), _p(out), dt, out.stride(0), out.stride(1), None, _stream()),
+               "ksb_sage_attn")
+    return out
+
+
+def sage_attention(q, k, v, sm_scale=None, tile_offsets=None, tile_entries=None, out=None):
+    """q [Lq,H,128], k,v [Lk,H,128] half -> [Lq,H,128]: K smoothing, INT8 Q/K, FP8 V, attention core."""
+    km = sage_kmean(k)
+    q8, qs = sage_quant_int8(q, Q_BLOCK, premul=q_premul(q.shape[-1], sm_scale))
+    k8, ks = sage_quant_int8(k, K_BLOCK, mean=km)
+    vt, vs = sage_quant_v(v)
+    return sage_attn_core(q8, qs, k8, ks, vt, vs, q.shape[0], k.shape[0], q.dtype, tile_offsets, tile_entries, out)

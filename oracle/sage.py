@@ -9,10 +9,17 @@ Arithmetic (the build's contract; the reference delegates it to the un-vendored
   V8, vs  = e4m3 per (head, channel) over tokens
   per 128-row Q block, KV tiles of 128 tokens visited in ascending order:
       X   = float(Q8 . K8^T) * (qs * ks)                      int32 dot, fp32 scale
-      m'  = max(m, rowmax X);  P = exp2(X - m');  a = exp2(m - m')
+      m'  = max(m, rowmax X);  P = exp2(X - m' + 8);  a = exp2(m - m')
       l   = l * a + rowsum(P)                                 fp32, P before rounding
       O   = O * a + float(e4m3(P)) . float(V8)                fp32 accumulate
   out = O / l * vs  -> input dtype
+
+P carries a fixed factor 2^8 (P_SHIFT): the row's largest P is exactly 256, which e4m3 holds
+exactly, and the bulk of a long, flat attention row lands in e4m3's normal range instead of its
+subnormals (the published SageAttention2 recipe scales P by a static factor for the same reason);
+the factor cancels in O / l.  The reference point m is the exact running row maximum, updated
+at every tile in which it grows -- an implementation has to rescale O at exactly those tiles to
+round P on the same e4m3 grid.
 
 Block-sparse variant: a tile mask [ceil(Lq/128), ceil(Lk/64)] (the reference's
 ``mask_id`` granularity, radial_sage_attn.py:155-160,174) removes whole
@@ -25,6 +32,8 @@ import torch
 import torch.nn.functional as F
 
 from . import quantizers as Qz
+
+P_SHIFT = 8.0  # log2 of the static scale applied to P before the e4m3 rounding
 
 
 def sdpa_reference(q, k, v, sm_scale=None):
@@ -70,7 +79,7 @@ def sage_core(pp, Lq, Lk, tile_mask=None, out_dtype=torch.float32):
         X = torch.where(valid, X, torch.full_like(X, float("-inf")))
         m_new = torch.maximum(m, X.amax(dim=-1))
         safe = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
-        P = torch.exp2(X - safe[..., None])
+        P = torch.exp2(X - safe[..., None] + P_SHIFT)
         a = torch.exp2(torch.where(torch.isinf(m), torch.full_like(m, float("-inf")), m - safe))
         l = l * a + P.sum(dim=-1)
         P8 = P.to(torch.float8_e4m3fn).float()
