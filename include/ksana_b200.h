@@ -107,6 +107,21 @@ int64_t ksb_sage_kmean_scratch_floats(int64_t L, int64_t H, int64_t D);
 int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
                    int64_t head_stride, float* partial, float* km, ksb_stream_t stream);
 
+/* Full-width RMSNorm with an fp32 weight, optionally followed by the 3-axis rotary embedding, in place
+ * on a [L, C] half view (row stride ld; e.g. the Q or K third of a fused QKV output), C = heads * 128.
+ * Replaces norm_q / norm_k (`x.float() * rsqrt(mean(x^2) + eps) * w`, ksana/operations/ops.py:64-70 via
+ * ksana/models/wan/wan_model.py:81-90,164-165) and apply_default_rope (ksana/utils/rope.py:62-128).
+ * rope_table: fp32 [table_len][64][2] = (cos, sin) of the reference's concatenated axis tables
+ * (wan_model.py:676-684); rotation pair p of a head reads axis f for p < nf, h for p < nf + nh, else w;
+ * row l sits at global position pos0 + l of an F x Hh x Ww grid, rows past the grid are not rotated.
+ * rope_table NULL = no rotation.  colsum_partial (fp32 scratch, ksb_rmsnorm_rope_scratch_floats) with
+ * colmean [C]: also returns the per-channel mean over the L rows of the values written (the K
+ * smoothing vector, sage_sla.py:198); both NULL to skip. */
+int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C);
+int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, float eps,
+                             const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww,
+                             int64_t pos0, float* colsum_partial, float* colmean, ksb_stream_t stream);
+
 /* INT8 block quantiser: xf = float(x) - mean[h,d] (if mean) then * premul (if premul != 0);
  * scale[h,b] = absmax(block)/127 (1 if zero); q = clamp(rint(xf/scale), +-127).
  * out: [H, Lpad, D] int8 with Lpad = roundup(L,128), padding zero-filled; scale: [H, Lpad/block].

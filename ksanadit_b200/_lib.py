@@ -32,6 +32,9 @@ SIGNATURES = {
     "ksb_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "ksb_sage_kmean_scratch_floats": (c_int64, [c_int64, c_int64, c_int64]),
     "ksb_sage_kmean": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "ksb_rmsnorm_rope_scratch_floats": (c_int64, [c_int64, c_int64]),
+    "ksb_rmsnorm_rope_inplace": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int, c_int,
+                                         c_int, c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "ksb_sage_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_void_p,
                                     c_void_p, c_void_p, c_void_p]),
     "ksb_sage_quant_v_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,

@@ -170,6 +170,116 @@ __global__ void __launch_bounds__(THREADS) v_quant_transpose_kernel(const T* __r
   }
 }
 
+
+// ---------------------------------------------------------------------------------- RMSNorm (+ RoPE) in place
+// Full-width RMSNorm over C = H*128 channels with an fp32 weight, optionally followed by the 3-axis
+// rotary embedding, applied in place to a [L, C] half view (row stride ld).  One CTA walks ROWS_PER_CTA
+// consecutive tokens; each thread owns fixed 8-channel vectors of the row, so it can also accumulate
+// the column sums of the values it writes (the K smoothing mean) without a second pass.
+// Rounding points follow the eager sequence: norm output rounded to half, rotation computed in fp32
+// (the eager path uses fp64) and rounded to half.
+constexpr int NR_THREADS = 256;
+constexpr int NR_MAX_VEC = 4;  // C <= 256 * 8 * 4 = 8192
+constexpr int NR_ROWS = 32;
+
+struct RopeGrid {
+  const float2* table;  // [table_len][64] (cos, sin); pair p of a head uses axis f for p < nf, then h, then w
+  int table_len, nf, nh;
+  int F, Hh, Ww;
+  int64_t pos0;  // global index of row 0 (sequence-parallel shard offset)
+};
+
+template <typename T, bool ROPE>
+__global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
+                                                                  const float* __restrict__ w, float eps, RopeGrid rg,
+                                                                  float* __restrict__ colsum_partial) {
+  __shared__ float red[NR_THREADS / 32];
+  const int nvec = C / 8;
+  const int64_t l0 = (int64_t)blockIdx.x * NR_ROWS;
+  const int64_t l1 = min(L, l0 + NR_ROWS);
+  float cs[NR_MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < NR_MAX_VEC; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) cs[i][e] = 0.f;
+  for (int64_t l = l0; l < l1; ++l) {
+    T* row = x + l * ld;
+    float v[NR_MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NR_MAX_VEC; ++i) {
+      const int j = threadIdx.x + i * NR_THREADS;
+      if (j < nvec) {
+        load8<T>(row + j * 8, v[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+      }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NR_THREADS / 32; ++i) tot += red[i];
+    const float rstd = rsqrtf(tot / (float)C + eps);
+    int cf = 0, ch = 0, cw = 0;
+    bool rotate = false;
+    if (ROPE) {
+      const int64_t pos = rg.pos0 + l;
+      const int64_t per_frame = (int64_t)rg.Hh * rg.Ww;
+      if (pos < (int64_t)rg.F * per_frame) {
+        rotate = true;
+        cf = (int)(pos / per_frame);
+        const int rem = (int)(pos - (int64_t)cf * per_frame);
+        ch = rem / rg.Ww;
+        cw = rem - ch * rg.Ww;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NR_MAX_VEC; ++i) {
+      const int j = threadIdx.x + i * NR_THREADS;
+      if (j < nvec) {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(v[i][e] * rstd * w[j * 8 + e]));
+        if (ROPE && rotate) {
+          const int p0 = ((j * 8) & (D - 1)) >> 1;  // first rotation pair of this vector inside its head
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const int pr = p0 + (e >> 1);
+            const int coord = pr < rg.nf ? cf : (pr < rg.nf + rg.nh ? ch : cw);
+            const float2 cssn = rg.table[(int64_t)coord * 64 + pr];
+            const float a = y[e], b = y[e + 1];
+            y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(a * cssn.x - b * cssn.y));
+            y[e + 1] = HalfOps<T>::to_f(HalfOps<T>::from_f(a * cssn.y + b * cssn.x));
+          }
+        }
+        uint4 o;
+        T* ot = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          ot[e] = HalfOps<T>::from_f(y[e]);
+          cs[i][e] += y[e];
+        }
+        *reinterpret_cast<uint4*>(row + j * 8) = o;
+      }
+    }
+  }
+  if (colsum_partial) {
+#pragma unroll
+    for (int i = 0; i < NR_MAX_VEC; ++i) {
+      const int j = threadIdx.x + i * NR_THREADS;
+      if (j < nvec) {
+        float* dst = colsum_partial + (int64_t)blockIdx.x * C + j * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(cs[i][0], cs[i][1], cs[i][2], cs[i][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(cs[i][4], cs[i][5], cs[i][6], cs[i][7]);
+      }
+    }
+  }
+}
+
 int validate(const void* x, int dtype, int64_t L, int64_t H, int64_t Dh, int64_t ts, int64_t hs) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (Dh != D) return fail(KSB_ERR_UNSUPPORTED, "head size %lld is not supported (only 128)", (long long)Dh);
@@ -206,6 +316,40 @@ int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, in
   const int HD = (int)(H * D);
   prep::mean_finish_kernel<<<(HD + 255) / 256, 256, 0, st>>>(partial, chunks, HD, 1.0f / (float)L, km);
   return check_launch("k mean (finish)");
+}
+
+
+int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C) {
+  return ((L + prep::NR_ROWS - 1) / prep::NR_ROWS) * C;
+}
+
+int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, float eps,
+                             const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
+                             float* colsum_partial, float* colmean, ksb_stream_t stream) {
+  if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
+  if (L <= 0 || C <= 0 || C % 128 != 0 || C > 256 * 8 * prep::NR_MAX_VEC) return fail(KSB_ERR_INVALID, "C=%lld must be a multiple of 128 and <= 8192", (long long)C);
+  if (!x || !w || !aligned16(x) || ld < C || ld % 8 != 0) return fail(KSB_ERR_INVALID, "x/w null, unaligned or bad row stride");
+  if ((colsum_partial == nullptr) != (colmean == nullptr)) return fail(KSB_ERR_INVALID, "colsum_partial and colmean go together");
+  if (colsum_partial && !aligned16(colsum_partial)) return fail(KSB_ERR_INVALID, "colsum_partial must be 16-byte aligned");
+  prep::RopeGrid rg{};
+  if (rope_table) {
+    if (nf < 0 || nh < 0 || nf + nh > 64 || F <= 0 || Hh <= 0 || Ww <= 0) return fail(KSB_ERR_INVALID, "bad rope grid");
+    if (F > table_len || Hh > table_len || Ww > table_len) return fail(KSB_ERR_INVALID, "rope table too short for the grid");
+    rg.table = reinterpret_cast<const float2*>(rope_table); rg.table_len = table_len; rg.nf = nf; rg.nh = nh;
+    rg.F = F; rg.Hh = Hh; rg.Ww = Ww; rg.pos0 = pos0;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int blocks = (int)((L + prep::NR_ROWS - 1) / prep::NR_ROWS);
+#define KSB_LAUNCH_NR(T, R) prep::rmsnorm_rope_kernel<T, R><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg, colsum_partial)
+  if (dtype == KSB_BF16) { if (rope_table) KSB_LAUNCH_NR(__nv_bfloat16, true); else KSB_LAUNCH_NR(__nv_bfloat16, false); }
+  else { if (rope_table) KSB_LAUNCH_NR(__half, true); else KSB_LAUNCH_NR(__half, false); }
+#undef KSB_LAUNCH_NR
+  if (int rc = check_launch("rmsnorm/rope")) return rc;
+  if (colsum_partial) {
+    prep::mean_finish_kernel<<<(int)((C + 255) / 256), 256, 0, st>>>(colsum_partial, blocks, (int)C, 1.0f / (float)L, colmean);
+    return check_launch("column mean");
+  }
+  return 0;
 }
 
 int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,

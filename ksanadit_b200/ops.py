@@ -14,6 +14,40 @@ Q_BLOCK, K_BLOCK, KV_TILE = 128, 64, 128
 LOG2E = 1.4426950408889634
 
 
+class LaunchStats:
+    """Counts the CUDA kernels this library launches and, when ``timing`` is on, brackets every call of a
+    chosen entry point with CUDA events on the launching stream (used by the benchmark's roofline)."""
+
+    def __init__(self):
+        self.kernels = 0
+        self.timing = False
+        self.events: dict = {}
+
+    def reset(self):
+        self.kernels = 0
+        self.events = {}
+
+    def count(self, n):
+        self.kernels += n
+
+    def timed(self, tag, fn):
+        if not self.timing:
+            return fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        self.events.setdefault(tag, []).append((a, b))
+        return r
+
+    def summary(self):
+        """tag -> (launches, total ms); call after a synchronize."""
+        return {t: (len(ev), sum(a.elapsed_time(b) for a, b in ev)) for t, ev in self.events.items()}
+
+
+STATS = LaunchStats()
+
+
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.bfloat16:
         return _lib.BF16
@@ -52,6 +86,7 @@ def quant_fp8_rowwise(x: torch.Tensor):
     s = torch.empty(M, dtype=torch.float32, device=x.device)
     _lib.check(_lib.load().ksb_quant_fp8_rowwise(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(q), _p(s), _stream()),
                "ksb_quant_fp8_rowwise")
+    STATS.count(1)
     return q, s
 
 
@@ -63,6 +98,7 @@ def quant_fp8_static(x: torch.Tensor, scale_input: torch.Tensor | None):
     s = torch.empty(M, dtype=torch.float32, device=x.device)
     _lib.check(_lib.load().ksb_quant_fp8_static(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(scale_input), _p(q), _p(s),
                                                 _stream()), "ksb_quant_fp8_static")
+    STATS.count(1)
     return q, s
 
 
@@ -79,6 +115,7 @@ def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False):
     _lib.check(_lib.load().ksb_adaln_quant_fp8(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(shift), _p(scale),
                                                shift.shape[0], float(eps), _p(h), _p(q), _p(s), _stream()),
                "ksb_adaln_quant_fp8")
+    STATS.count(1)
     return (q, s, h) if want_h else (q, s)
 
 
@@ -92,6 +129,7 @@ def layernorm_quant_fp8(x, w, b, eps=1e-6, want_h=False):
     h = torch.empty(M, K, dtype=x.dtype, device=x.device) if want_h else None
     _lib.check(_lib.load().ksb_layernorm_quant_fp8(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(w), _p(b), float(eps),
                                                    _p(h), _p(q), _p(s), _stream()), "ksb_layernorm_quant_fp8")
+    STATS.count(1)
     return (q, s, h) if want_h else (q, s)
 
 
@@ -115,9 +153,11 @@ def fp8_gemm(a_q, a_scale, w_q, w_scale, bias=None, out_dtype=torch.bfloat16, ep
         gate = gate.reshape(-1, N).to(out.dtype).contiguous()
         gate_rows = gate.shape[0]
         ldr = resid.stride(0) if M > 1 else N
-    _lib.check(_lib.load().ksb_fp8_gemm(_p(a_q), _p(a_scale), _p(w_q), _p(w_scale), _p(bias), M, N, K, _p(out), dt,
-                                        out.stride(0) if M > 1 else N, epilogue, _p(resid), ldr, _p(gate), gate_rows, _stream()),
-               "ksb_fp8_gemm")
+    STATS.timed(("gemm", M, N, K), lambda: _lib.check(
+        _lib.load().ksb_fp8_gemm(_p(a_q), _p(a_scale), _p(w_q), _p(w_scale), _p(bias), M, N, K, _p(out), dt,
+                                 out.stride(0) if M > 1 else N, epilogue, _p(resid), ldr, _p(gate), gate_rows, _stream()),
+        "ksb_fp8_gemm"))
+    STATS.count(1)
     return out
 
 
@@ -128,6 +168,7 @@ def gate_residual(x, y, gate):
     out = torch.empty_like(x)
     _lib.check(_lib.load().ksb_gate_residual(_p(x.contiguous()), _p(y.contiguous()), _p(gate), gate.shape[0], _p(out), _dt(x), M, N,
                                              _stream()), "ksb_gate_residual")
+    STATS.count(1)
     return out
 
 
@@ -147,6 +188,7 @@ def sage_kmean(k):
     partial = torch.empty(lib.ksb_sage_kmean_scratch_floats(L, H, D), dtype=torch.float32, device=k.device)
     km = torch.empty(H, D, dtype=torch.float32, device=k.device)
     _lib.check(lib.ksb_sage_kmean(_p(k), _dt(k), L, H, D, ts, hs, _p(partial), _p(km), _stream()), "ksb_sage_kmean")
+    STATS.count(2)
     return km
 
 
@@ -159,6 +201,7 @@ def sage_quant_int8(x, block, premul=0.0, mean=None):
     sc = torch.empty(H, Lp // block, dtype=torch.float32, device=x.device)
     _lib.check(_lib.load().ksb_sage_quant_int8(_p(x), _dt(x), L, H, D, ts, hs, block, float(premul), _p(mean), _p(out), _p(sc),
                                                _stream()), "ksb_sage_quant_int8")
+    STATS.count(1)
     return out, sc
 
 
@@ -172,6 +215,7 @@ def sage_quant_v(v):
     vs = torch.empty(H, D, dtype=torch.float32, device=v.device)
     _lib.check(_lib.load().ksb_sage_quant_v_fp8(_p(v), _dt(v), L, H, D, ts, hs, _p(amax), _p(vt), _p(vs), _stream()),
                "ksb_sage_quant_v_fp8")
+    STATS.count(2)
     return vt, vs
 
 
@@ -188,9 +232,11 @@ def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, til
         out = torch.empty(Lq, H, 128, dtype=out_dtype, device=q8.device)
     assert out.stride(2) == 1
     dt = _lib.BF16 if out.dtype == torch.bfloat16 else _lib.FP16
-    _lib.check(_lib.load().ksb_sage_attn(_p(q8), _p(qs), _p(k8), _p(ks), _p(vt), _p(vs), H, Lq, Lk, _p(tile_offsets),
-                                         _p(tile_entries), _p(out), dt, out.stride(0), out.stride(1), None, _stream()),
-               "ksb_sage_attn")
+    STATS.timed(("attn", H, Lq, Lk, tile_offsets is not None), lambda: _lib.check(
+        _lib.load().ksb_sage_attn(_p(q8), _p(qs), _p(k8), _p(ks), _p(vt), _p(vs), H, Lq, Lk, _p(tile_offsets),
+                                  _p(tile_entries), _p(out), dt, out.stride(0), out.stride(1), None, _stream()),
+        "ksb_sage_attn"))
+    STATS.count(1)
     return out
 
 
@@ -201,3 +247,54 @@ def sage_attention(q, k, v, sm_scale=None, tile_offsets=None, tile_entries=None,
     k8, ks = sage_quant_int8(k, K_BLOCK, mean=km)
     vt, vs = sage_quant_v(v)
     return sage_attn_core(q8, qs, k8, ks, vt, vs, q.shape[0], k.shape[0], q.dtype, tile_offsets, tile_entries, out)
+
+
+# ----------------------------------------------------------------------------- RMSNorm + RoPE (in place)
+
+_ROPE_TABLES: dict = {}
+
+
+def wan_rope_table(head_dim: int = 128, max_len: int = 1024, theta: float = 10000.0, device="cuda"):
+    """(cos, sin) table fp32 [max_len, head_dim//2, 2] of Wan's concatenated axis tables, plus (n_f, n_h).
+
+    Same construction as KsanaDiT's ``rope_params`` x3 (ksana/models/wan/wan_model.py:51-58,676-684):
+    computed in fp64, stored in fp32.  Host-side set-up, cached per (head_dim, max_len, theta, device).
+    """
+    key = (head_dim, max_len, theta, str(device))
+    if key not in _ROPE_TABLES:
+        d = head_dim
+        dims = [d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6)]
+        pos = torch.arange(max_len, dtype=torch.float64)
+        cols = []
+        for dd in dims:
+            inv = 1.0 / torch.pow(theta, torch.arange(0, dd, 2, dtype=torch.float64) / dd)
+            cols.append(torch.outer(pos, inv))
+        ang = torch.cat(cols, dim=1)
+        tab = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous()
+        _ROPE_TABLES[key] = (tab.to(device), dims[0] // 2, dims[1] // 2)
+    return _ROPE_TABLES[key]
+
+
+def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean=False):
+    """x: [L, C] half view (row stride allowed), normalised (and rotated) in place.
+
+    rope: result of wan_rope_table or None; grid: (F, H, W).  Returns the fp32 column mean [C] of the
+    written values when want_mean.
+    """
+    _cuda(x, w)
+    assert x.dim() == 2 and x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous()
+    L, C = x.shape
+    lib = _lib.load()
+    partial = mean = None
+    if want_mean:
+        partial = torch.empty(lib.ksb_rmsnorm_rope_scratch_floats(L, C), dtype=torch.float32, device=x.device)
+        mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    tab, tlen, nf, nh, F, Hh, Ww = None, 0, 0, 0, 1, 1, 1
+    if rope is not None:
+        tab, nf, nh = rope
+        tlen = tab.shape[0]
+        F, Hh, Ww = (int(v) for v in grid)
+    _lib.check(lib.ksb_rmsnorm_rope_inplace(_p(x), _dt(x), L, C, x.stride(0) if L > 1 else C, _p(w), float(eps), _p(tab), tlen, nf, nh,
+                                            F, Hh, Ww, int(pos0), _p(partial), _p(mean), _stream()), "ksb_rmsnorm_rope_inplace")
+    STATS.count(2 if want_mean else 1)
+    return mean

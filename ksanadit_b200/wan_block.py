@@ -1,0 +1,233 @@
+"""Wan DiT block on the B200 kernels: the fused form of ``WanAttentionBlock.forward``.
+
+Takes the same inputs and holds the same parameters (same state-dict names) as KsanaDiT's
+``WanAttentionBlock`` / ``WanSelfAttention`` / ``WanCrossAttention``
+(ksana/models/wan/wan_model.py:61-393), but runs the block as the kernel sequence
+
+  adaLN+quant -> QKV GEMM -> RMSNorm+RoPE (in place) -> [Ulysses all-to-all] -> Sage quantisers ->
+  INT8/FP8 attention -> [all-to-all] -> quant -> o-proj GEMM (+gated residual) ->
+  LayerNorm+quant -> cross-attention (q GEMM, cached context K/V, attention, o GEMM + residual) ->
+  adaLN+quant -> FFN-up GEMM (+GELU) -> quant -> FFN-down GEMM (+gated residual)
+
+so that every elementwise pass of the eager block is fused into a quantiser or a GEMM epilogue.
+torch is used for buffers, views and the NCCL exchange only.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib, distribute, ops
+from .linear import B200Fp8Linear, quantize_weight_per_channel
+
+HEAD = 128
+
+
+class B200WanBlock(torch.nn.Module):
+    def __init__(self, dim, ffn_dim, num_heads, block_id=0, eps=1e-6, cross_attn_norm=True, device="cuda",
+                 dtype=torch.bfloat16, tile_lists=None, cache_context=False):
+        super().__init__()
+        if dim != num_heads * HEAD:
+            raise _lib.KsanaB200Error(f"head size {dim // num_heads} is not supported (only {HEAD})")
+        self.dim, self.ffn_dim, self.num_heads, self.block_id, self.eps = dim, ffn_dim, num_heads, block_id, eps
+        self.dtype = dtype
+        kw = dict(device=device, dtype=dtype)
+        self.self_attn = torch.nn.Module()
+        self.self_attn.qkv = B200Fp8Linear(dim, 3 * dim, **kw)
+        self.self_attn.o = B200Fp8Linear(dim, dim, **kw)
+        self.self_attn.norm_q = torch.nn.Module()
+        self.self_attn.norm_k = torch.nn.Module()
+        self.cross_attn = torch.nn.Module()
+        for n in "qkvo":
+            setattr(self.cross_attn, n, B200Fp8Linear(dim, dim, **kw))
+        self.cross_attn.norm_q = torch.nn.Module()
+        self.cross_attn.norm_k = torch.nn.Module()
+        for m in (self.self_attn.norm_q, self.self_attn.norm_k, self.cross_attn.norm_q, self.cross_attn.norm_k):
+            m.weight = torch.nn.Parameter(torch.ones(dim, device=device, dtype=torch.float32), requires_grad=False)
+        self.norm3 = torch.nn.Module()
+        self.norm3.weight = torch.nn.Parameter(torch.ones(dim, device=device, dtype=torch.float32), requires_grad=False)
+        self.norm3.bias = torch.nn.Parameter(torch.zeros(dim, device=device, dtype=torch.float32), requires_grad=False)
+        self.cross_attn_norm = cross_attn_norm
+        self.ffn = torch.nn.ModuleList([B200Fp8Linear(dim, ffn_dim, **kw), torch.nn.Identity(), B200Fp8Linear(ffn_dim, dim, **kw)])
+        self.modulation = torch.nn.Parameter(torch.zeros(1, 6, dim, device=device, dtype=dtype), requires_grad=False)
+        self.tile_lists = tile_lists  # (offsets, entries) for block-sparse self-attention, or None
+        self.cache_context = cache_context  # keep the quantised context K/V across steps (off: recomputed every call)
+        self._ones = None
+        self._ctx_cache = None
+
+    # ------------------------------------------------------------------ parameter loading
+    @staticmethod
+    def _set_linear(lin: B200Fp8Linear, w, b, scale=None):
+        if w.dtype == torch.float8_e4m3fn:
+            wq, s = w, (torch.ones((), dtype=torch.float32) if scale is None else scale.float())
+        else:
+            wq, s = quantize_weight_per_channel(w.to(lin.weight.device))
+        lin.weight = torch.nn.Parameter(wq.to(lin.weight.device).contiguous(), requires_grad=False)
+        lin.scale_weight = torch.nn.Parameter(s.to(lin.weight.device), requires_grad=False)
+        lin._w_scale_vec = None
+        if b is not None:
+            lin.bias = torch.nn.Parameter(b.to(lin.weight.device, lin.compute_dtype), requires_grad=False)
+
+    def load_block_state_dict(self, sd: dict):
+        """Loads a state dict with WanAttentionBlock's names.  High-precision weights are quantised per output
+        channel; fp8 weights are taken as they are with their ``scale_weight``.  Separate q/k/v are fused."""
+        sd = dict(sd)
+        from .fuse_qkv import MODEL_QKV_PATTERNS, remap_qkv_weights
+        if "self_attn.q.weight" in sd and sd["self_attn.q.weight"].dtype != torch.float8_e4m3fn:
+            for n in "qkv":  # quantise before fusing so that each projection keeps its own channel scales
+                wq, s = quantize_weight_per_channel(sd["self_attn." + n + ".weight"].to(self.modulation.device))
+                sd["self_attn." + n + ".weight"], sd["self_attn." + n + ".scale_weight"] = wq, s
+        remap_qkv_weights(sd, [tuple(p.lstrip(".") for p in MODEL_QKV_PATTERNS["wan"][0])])
+        for name, lin in (("self_attn.qkv", self.self_attn.qkv), ("self_attn.o", self.self_attn.o), ("cross_attn.q", self.cross_attn.q),
+                          ("cross_attn.k", self.cross_attn.k), ("cross_attn.v", self.cross_attn.v), ("cross_attn.o", self.cross_attn.o),
+                          ("ffn.0", self.ffn[0]), ("ffn.2", self.ffn[2])):
+            self._set_linear(lin, sd[name + ".weight"], sd.get(name + ".bias"), sd.get(name + ".scale_weight"))
+        dev = self.modulation.device
+        for name, mod in (("self_attn.norm_q", self.self_attn.norm_q), ("self_attn.norm_k", self.self_attn.norm_k),
+                          ("cross_attn.norm_q", self.cross_attn.norm_q), ("cross_attn.norm_k", self.cross_attn.norm_k)):
+            mod.weight = torch.nn.Parameter(sd[name + ".weight"].float().to(dev).contiguous(), requires_grad=False)
+        if "norm3.weight" in sd:
+            self.norm3.weight = torch.nn.Parameter(sd["norm3.weight"].float().to(dev).contiguous(), requires_grad=False)
+            self.norm3.bias = torch.nn.Parameter(sd["norm3.bias"].float().to(dev).contiguous(), requires_grad=False)
+        self.modulation = torch.nn.Parameter(sd["modulation"].to(dev, self.dtype), requires_grad=False)
+        self._ctx_cache = None
+        return self
+
+    def random_init(self, seed: int, std: float = 0.02, qk_offset: float = 0.5):
+        """Random-init weights of this architecture, drawn on the device (weights ~ N(0, std)); the Q and K
+        projections get a per-channel bias ~ N(0, qk_offset) so that K smoothing has a mean to remove."""
+        g = torch.Generator(device=self.modulation.device).manual_seed(seed)
+        dev = self.modulation.device
+
+        def W(n, k):
+            return (torch.randn(n, k, device=dev, generator=g) * std).to(self.dtype)
+
+        def V(n, s=std):
+            return (torch.randn(n, device=dev, generator=g) * s)
+
+        for lin in (self.self_attn.qkv, self.self_attn.o, self.cross_attn.q, self.cross_attn.k, self.cross_attn.v, self.cross_attn.o,
+                    self.ffn[0], self.ffn[2]):
+            self._set_linear(lin, W(lin.out_features, lin.in_features), V(lin.out_features).to(self.dtype))
+        if qk_offset:
+            self.self_attn.qkv.bias.data[: 2 * self.dim] = V(2 * self.dim, qk_offset).to(self.dtype)
+        for mod in (self.self_attn.norm_q, self.self_attn.norm_k, self.cross_attn.norm_q, self.cross_attn.norm_k, self.norm3):
+            mod.weight = torch.nn.Parameter((1 + V(self.dim, 0.1)).float(), requires_grad=False)
+        self.norm3.bias = torch.nn.Parameter(V(self.dim, 0.1).float(), requires_grad=False)
+        self.modulation = torch.nn.Parameter((torch.randn(1, 6, self.dim, device=dev, generator=g) * 0.1).to(self.dtype), requires_grad=False)
+        self._ctx_cache = None
+        return self
+
+    # ------------------------------------------------------------------ pieces
+    def _context_kv(self, context):
+        """Quantised cross-attention K / V of the text context.  They depend only on the block's weights and
+        the prompt; with ``cache_context`` they are kept across denoise steps while the same context tensor is
+        passed (the reference recomputes them every step, wan_model.py:237-238, and so does the default here)."""
+        key = (context.data_ptr(), context._version, tuple(context.shape))
+        if self.cache_context and self._ctx_cache is not None and self._ctx_cache[0] == key:
+            return self._ctx_cache[1]
+        ca = self.cross_attn
+        Lc = context.shape[0]
+        k = ca.k(context)
+        ops.rmsnorm_rope_inplace(k, ca.norm_k.weight, self.eps)
+        v = ca.v(context)
+        k3, v3 = k.view(Lc, self.num_heads, HEAD), v.view(Lc, self.num_heads, HEAD)
+        km = ops.sage_kmean(k3)
+        k8, ks = ops.sage_quant_int8(k3, ops.K_BLOCK, mean=km)
+        vt, vs = ops.sage_quant_v(v3)
+        val = (k8, ks, vt, vs, Lc)
+        self._ctx_cache = (key, val)
+        return val
+
+    def _self_attention(self, xq, sx, L, grid, rope):
+        C, H = self.dim, self.num_heads
+        P, rank = distribute.get_world_size(), distribute.get_rank_id()
+        sa = self.self_attn
+        qkv = sa.qkv.forward_quantized(xq, sx, self.dtype)  # [L, 3C]
+        km = ops.rmsnorm_rope_inplace(qkv[:, C:2 * C], sa.norm_k.weight, self.eps, rope, grid, pos0=rank * L, want_mean=(P == 1))
+        ops.rmsnorm_rope_inplace(qkv[:, :C], sa.norm_q.weight, self.eps, rope, grid, pos0=rank * L)
+        if P > 1:
+            g = distribute.heads_to_sequence(qkv.view(L, 3, H, HEAD))  # [L*P, 3, H/P, D]
+            q3, k3, v3 = g[:, 0], g[:, 1], g[:, 2]
+            km = ops.sage_kmean(k3)
+        else:
+            t = qkv.view(L, 3, H, HEAD)
+            q3, k3, v3 = t[:, 0], t[:, 1], t[:, 2]
+            km = km.view(H, HEAD)
+        Lf = q3.shape[0]
+        q8, qs = ops.sage_quant_int8(q3, ops.Q_BLOCK, premul=ops.q_premul(HEAD))
+        k8, ks = ops.sage_quant_int8(k3, ops.K_BLOCK, mean=km)
+        vt, vs = ops.sage_quant_v(v3)
+        offs, ents = self.tile_lists if self.tile_lists is not None else (None, None)
+        o = ops.sage_attn_core(q8, qs, k8, ks, vt, vs, Lf, Lf, self.dtype, offs, ents)  # [L*P, H/P, D]
+        if P > 1:
+            o = distribute.sequence_to_heads(o)  # [L, H, D]
+        return o.reshape(L, C)
+
+    def _block_one(self, x, e6, context, grid, rope):
+        """x [L, C]; e6 six [1, C] or [L, C] tensors (modulation already added); context [Lc, C]."""
+        L, C = x.shape
+        if self._ones is None or self._ones.device != x.device:
+            self._ones = torch.ones(1, C, dtype=self.dtype, device=x.device)
+        # self-attention
+        xq, sx = ops.adaln_quant_fp8(x, e6[0], e6[1], self.eps)
+        a = self._self_attention(xq, sx, L, grid, rope)
+        aq, sa = ops.quant_fp8_rowwise(a)
+        x = self.self_attn.o.forward_quantized(aq, sa, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=e6[2])
+        # cross-attention
+        ca = self.cross_attn
+        if self.cross_attn_norm:
+            hq, hs = ops.layernorm_quant_fp8(x, self.norm3.weight, self.norm3.bias, self.eps)
+        else:
+            hq, hs = ops.quant_fp8_rowwise(x)
+        q = ca.q.forward_quantized(hq, hs, self.dtype)
+        ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
+        k8, ks, vt, vs, Lc = self._context_kv(context)
+        q8, qs = ops.sage_quant_int8(q.view(L, self.num_heads, HEAD), ops.Q_BLOCK, premul=ops.q_premul(HEAD))
+        o = ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, Lc, self.dtype).view(L, C)
+        oq, os_ = ops.quant_fp8_rowwise(o)
+        x = ca.o.forward_quantized(oq, os_, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=self._ones, out=x)
+        # FFN
+        xq, sx = ops.adaln_quant_fp8(x, e6[3], e6[4], self.eps)
+        h = self.ffn[0].forward_quantized(xq, sx, self.dtype, _lib.EPI_GELU_TANH)
+        hq, hs = ops.quant_fp8_rowwise(h)
+        x = self.ffn[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=e6[5], out=x)
+        return x
+
+    # ------------------------------------------------------------------ WanAttentionBlock.forward signature
+    def forward(self, x, e, seq_lens=None, grid_sizes=None, freqs=None, context=None, context_lens=None, step_iter=None,
+                latent_shape=None, rope_func="default", **_):
+        """x [B, L, C]; e [B, 1, 6, C] (or [B, L, 6, C]); grid_sizes [B, 3] (F, H, W); context [B, Lc, C].
+        ``freqs`` is accepted for signature compatibility; the rotation table is rebuilt from the same formula."""
+        if rope_func != "default":
+            raise _lib.KsanaB200Error("only the default (complex) RoPE formulation is implemented")
+        if x.dtype != self.dtype:
+            raise TypeError(f"block built for {self.dtype}, got {x.dtype}")
+        B = x.shape[0]
+        rope = ops.wan_rope_table(HEAD, 1024, device=x.device)
+        em = (self.modulation.unsqueeze(0) + e) if e.dim() == 4 else (self.modulation + e).unsqueeze(1)  # [B, 1|L, 6, C]
+        em = em.to(self.dtype)
+        outs = []
+        for b in range(B):
+            e6 = [em[b, :, i].contiguous() for i in range(6)]
+            grid = tuple(int(v) for v in (grid_sizes[b].tolist() if torch.is_tensor(grid_sizes) else grid_sizes[b]))
+            outs.append(self._block_one(x[b], e6, context[b], grid, rope))
+        return torch.stack(outs) if B > 1 else outs[0].unsqueeze(0)
+
+
+class B200WanDenoiseStep(torch.nn.Module):
+    """The per-step hot loop of WanModel: ``for block in self.blocks: x = block(x, ...)`` (wan_model.py:785-793)
+    over a token shard, for a Wan-shaped stack of blocks."""
+
+    def __init__(self, num_layers, dim, ffn_dim, num_heads, device="cuda", dtype=torch.bfloat16, tile_lists=None, seed=0,
+                 cache_context=False):
+        super().__init__()
+        self.blocks = torch.nn.ModuleList(
+            [B200WanBlock(dim, ffn_dim, num_heads, block_id=i, device=device, dtype=dtype, tile_lists=tile_lists,
+                          cache_context=cache_context).random_init(seed + i)
+             for i in range(num_layers)]
+        )
+
+    def forward(self, x, e, grid_sizes, context):
+        for blk in self.blocks:
+            x = blk(x, e, grid_sizes=grid_sizes, context=context)
+        return x
