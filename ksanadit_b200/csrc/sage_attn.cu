@@ -1,6 +1,6 @@
 // Sage-style quantised attention core on the Blackwell tensor cores, dense or block-sparse.
 //
-//   S = Q8 . K8^T            tcgen05.mma kind::i8   (s32 accumulator in tensor memory)
+//   S = Q8 . K8^T            tcgen05.mma kind::i8   (s32 accumulator in tensor memory, see below)
 //   X = float(S) * qs * ks   fp32, exp2 domain (softmax scale and log2 e are folded into Q8's scale)
 //   P = exp2(X - m + 8)      fp32 online softmax against the exact running row maximum, rounded to e4m3
 //   O += P . V8              tcgen05.mma kind::f8f6f4 (f32 accumulator in tensor memory)
@@ -15,6 +15,9 @@
 //   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written to shared memory
 //               in the 128-byte-swizzled K-major layout the MMA reads, O rescaled in tensor memory in the
 //               tiles where a row maximum of the warp grew; final normalisation and store
+// The s32 score accumulator is pre-loaded with 0x4B400000 before every S = Q.K^T and the MMA accumulates
+// on top of it: the bit pattern read back, taken as an fp32, is exactly 12582912 + S (|S| < 2^22), so the
+// scores need no integer-to-float conversion and X = fma(bits_as_float, scale, -12582912 * scale - m + 8).
 // Every mbarrier wait is bounded (see common.cuh).
 //
 // Tensor-bound: 4 * 128 * 128 * 128 flop per visited (Q block, KV tile) pair.
@@ -32,6 +35,8 @@ constexpr int TILE_BYTES = 128 * 128;
 constexpr int THREADS = 256;
 constexpr int TMEM_COLS = 256;  // S: columns 0..127 (s32), O: columns 128..255 (f32)
 constexpr int KERNEL_ID = 2;
+constexpr uint32_t S_MAGIC_BITS = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23: one ulp is 1 on [2^23, 2^24)
+constexpr float S_MAGIC = 12582912.0f;
 constexpr float P_SHIFT = 8.0f;  // P carries a static factor 2^8 into e4m3: the row maximum maps to 256 exactly
 constexpr int NUM_BARS = 12;
 constexpr int SMEM_BYTES = 1024 + (2 + KST + VST) * TILE_BYTES + 8 * NUM_BARS + 64;
@@ -68,6 +73,38 @@ __device__ __forceinline__ Work get_work(const Params& p, int idx) {
   return w;
 }
 __device__ __forceinline__ int entry_at(const Work& w, int j) { return w.ents ? w.ents[j] : (j * 4 + 3); }
+
+
+// Max over 64 scores (as floats) held in two 32-register chunks: four independent chains, each step
+// folding two new values with a three-input max.
+__device__ __forceinline__ float tree_max64(const uint32_t (&a)[32], const uint32_t (&b)[32]) {
+  float m0 = fmaxf(__uint_as_float(a[0]), __uint_as_float(a[1])), m1 = fmaxf(__uint_as_float(a[2]), __uint_as_float(a[3]));
+  float m2 = fmaxf(__uint_as_float(b[0]), __uint_as_float(b[1])), m3 = fmaxf(__uint_as_float(b[2]), __uint_as_float(b[3]));
+#pragma unroll
+  for (int i = 4; i < 32; i += 4) {
+    m0 = fmax3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+    m1 = fmax3(m1, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
+    m2 = fmax3(m2, __uint_as_float(b[i]), __uint_as_float(b[i + 1]));
+    m3 = fmax3(m3, __uint_as_float(b[i + 2]), __uint_as_float(b[i + 3]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// P = exp2(f * sc + c) for one 32-score chunk (f = 12582912 + S as fp32) -> 8 words of packed e4m3; the
+// exact (unrounded) values are added into four independent packed accumulators.  A masked score holds -inf
+// and yields exactly 0.
+__device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], float sc, float c, uint32_t* pk, float2 (&acc)[4]) {
+  const float2 sc2 = make_float2(sc, sc), c2 = make_float2(c, c);
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, c2);
+    const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc2, c2);
+    const float e0 = fast_exp2(x01.x), e1 = fast_exp2(x01.y), e2 = fast_exp2(x23.x), e3 = fast_exp2(x23.y);
+    acc[(i >> 2) & 3] = __fadd2_rn(acc[(i >> 2) & 3], make_float2(e0, e1));
+    acc[((i >> 2) + 2) & 3] = __fadd2_rn(acc[((i >> 2) + 2) & 3], make_float2(e2, e3));
+    pk[i >> 2] = cvt_e4m3x4(e0, e1, e2, e3);
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -110,7 +147,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&tmap_q);
@@ -153,11 +190,11 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       auto issue_qk = [&](uint32_t gg) -> bool {
         const uint32_t s = itk % KST, ph = (itk / KST) & 1;
         if (!mbar_wait(k_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 4)) return false;
-        if (!mbar_wait(s_empty, (gg & 1) ^ 1, p.status, (KERNEL_ID << 16) | 5)) return false;
+        if (!mbar_wait(s_empty, gg & 1, p.status, (KERNEL_ID << 16) | 5)) return false;  // S pre-loaded (completion #gg)
         tc_fence_after();
         const uint64_t dk = make_kmajor_sw128_desc(k_smem + s * TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < D / UMMA_K; ++kk) mma_i8_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_qk, kk != 0);
+        for (int kk = 0; kk < D / UMMA_K; ++kk) mma_i8_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_qk, 1);  // on top of the pre-load
         mma_commit(s_full);
         mma_commit(k_empty + 8 * s);
         ++itk;
@@ -190,7 +227,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // ------------------------------------------------------------------ softmax warps (one row per thread)
     const int qrt = warp & 3;
     const int row = qrt * 32 + lane;
@@ -199,6 +236,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     T* out = static_cast<T*>(p.out);
     uint32_t g = 0;
     bool ok = true;
+    // pre-load the score accumulator for the first S = Q.K^T (completion #0 of s_empty)
+#pragma unroll
+    for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(s_empty);
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
       const Work w = get_work(p, idx);
       const int qrow = w.qt * BQ + row;
@@ -212,8 +255,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       const float qsc = p.qs[w.h * p.nq + w.qt];
       float m_used = -INFINITY, l = 0.f;
+      // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
+      int e_next = entry_at(w, 0);
+      float ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)], ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
       for (int j = 0; j < w.n; ++j) {
-        const int e = entry_at(w, j);
+        const int e = e_next;
+        const float sc0 = qsc * ks0_next, sc1 = qsc * ks1_next;
+        if (j + 1 < w.n) {
+          e_next = entry_at(w, j + 1);
+          ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)];
+          ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
+        }
         const int t = e >> 2, halves = e & 3;
         const int valid = min(BKV, p.Lk - t * BKV);
         const bool full = (halves == 3) && (valid == BKV);
@@ -225,82 +277,49 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld32(tmem_s + lane_sel + 64, s[2]);
         tmem_ld32(tmem_s + lane_sel + 96, s[3]);
         tmem_wait_ld();
+        // pre-load the accumulator for the next S = Q.K^T, then hand it back to the MMA issuer
+#pragma unroll
+        for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
+        tmem_wait_st();
         tc_fence_before();
         mbar_arrive(s_empty);
-        const float sc0 = qsc * p.ks[w.h * nk64 + 2 * t], sc1 = qsc * p.ks[w.h * nk64 + 2 * t + 1];
         if (!full) {
-          // masked columns (ragged tail or dropped 64-token half) take the most negative score
+          // masked columns (ragged tail or dropped 64-token half) become -inf: never the maximum, P = 0
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int col = c * 32 + i;
               const bool keep = (col < valid) && ((halves >> (col >> 6)) & 1);
-              if (!keep) s[c][i] = 0x80000000u;
+              if (!keep) s[c][i] = 0xff800000u;
             }
         }
-        int mx0 = INT_MIN, mx1 = INT_MIN;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          mx0 = max(mx0, max(static_cast<int>(s[0][i]), static_cast<int>(s[1][i])));
-          mx1 = max(mx1, max(static_cast<int>(s[2][i]), static_cast<int>(s[3][i])));
-        }
-        float m_tile = -INFINITY;
-        if (mx0 != INT_MIN) m_tile = __int2float_rn(mx0) * sc0;
-        if (mx1 != INT_MIN) m_tile = fmaxf(m_tile, __int2float_rn(mx1) * sc1);
-        // the reference point is the exact running maximum: O is rescaled in every tile in which some row
-        // of the warp found a larger score (rows that did not get the factor 1)
-        const bool grow = m_tile > m_used;  // also true for the first tile (m_used = -inf)
-        bool waited_pv = false;
-        if (__any_sync(0xffffffffu, grow)) {
+        // exact: both operands of the subtraction are integers below 2^24
+        const float m_tile = fmaxf((tree_max64(s[0], s[1]) - S_MAGIC) * sc0, (tree_max64(s[2], s[3]) - S_MAGIC) * sc1);
+        // The reference point is the exact running maximum: O and l are rescaled in every tile in which some
+        // row of the warp found a larger score (rows that did not get the factor 1).
+        const bool grow = m_tile > m_used;  // also true for the first tile with a valid score (m_used = -inf)
+        const bool rescale = __any_sync(0xffffffffu, grow);
+        float alpha = 1.f;
+        if (rescale) {
           const float m_new = fmaxf(m_used, m_tile);
-          const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
-          if (j > 0) {
-            // O may only be touched once the previous P.V has completed
-            if (!mbar_wait_warp(p_empty, (g & 1) ^ 1, p.status, (KERNEL_ID << 16) | 10)) { ok = false; break; }
-            waited_pv = true;
-            tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-              uint32_t o[32];
-              tmem_ld32(tmem_o + lane_sel + c, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(tmem_o + lane_sel + c, o);
-            }
-            tmem_wait_st();
-          }
+          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
           l *= alpha;
           m_used = m_new;
         }
-        // P = exp2(X - m_used) -> e4m3, packed 4 per word; masked columns give exactly 0
+        // P = exp2(X - m_used + 8) -> e4m3, packed 4 per word; masked columns give exactly 0
         const float neg_m = (m_used == -INFINITY) ? 0.f : (P_SHIFT - m_used);
         uint32_t pk[32];
-        float lsum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float sc = (c < 2) ? sc0 : sc1;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float pv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int si = static_cast<int>(s[c][i + u]);
-              float x = fmaf(__int2float_rn(si), sc, neg_m);
-              float e2 = fast_exp2(x);
-              if (!full && si == INT_MIN) e2 = 0.f;
-              pv[u] = e2;
-              lsum += e2;
-            }
-            pk[c * 8 + (i >> 2)] = cvt_e4m3x4(pv[0], pv[1], pv[2], pv[3]);
-          }
-        }
-        l += lsum;
-        if (!waited_pv) {
-          // the previous P.V must have finished reading the P buffer before it is overwritten
-          if (!mbar_wait_warp(p_empty, (g & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
-        }
+        float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const float c0 = fmaf(-S_MAGIC, sc0, neg_m), c1 = fmaf(-S_MAGIC, sc1, neg_m);
+        exp_chunk(s[0], sc0, c0, pk, acc);
+        exp_chunk(s[1], sc0, c0, pk + 8, acc);
+        exp_chunk(s[2], sc1, c1, pk + 16, acc);
+        exp_chunk(s[3], sc1, c1, pk + 24, acc);
+        l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+        // the previous P.V must have finished: it read the P buffer that is overwritten now and wrote the O
+        // accumulator that is rescaled below
+        if (!mbar_wait_warp(p_empty, (g & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
         // row `row` of the K-major tile: eight 16-byte chunks, chunk index XORed with (row & 7)
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -308,6 +327,28 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           *reinterpret_cast<uint4*>(p_gen + row * 128 + ((c ^ (row & 7)) << 4)) = v4;
         }
         fence_proxy_async_smem();
+        if (rescale && j > 0) {
+          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now)
+          tc_fence_after();
+          uint32_t o[4][32];
+          tmem_ld32(tmem_o + lane_sel + 0, o[0]);
+          tmem_ld32(tmem_o + lane_sel + 32, o[1]);
+          tmem_ld32(tmem_o + lane_sel + 64, o[2]);
+          tmem_ld32(tmem_o + lane_sel + 96, o[3]);
+          tmem_wait_ld();
+          const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float2 r = __fmul2_rn(make_float2(__uint_as_float(o[c][i]), __uint_as_float(o[c][i + 1])), a2);
+              o[c][i] = __float_as_uint(r.x);
+              o[c][i + 1] = __float_as_uint(r.y);
+            }
+            tmem_st32(tmem_o + lane_sel + 32 * c, o[c]);
+          }
+          tmem_wait_st();
+        }
         tc_fence_before();
         mbar_arrive(p_full);
         ++g;

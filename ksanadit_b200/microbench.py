@@ -1,0 +1,139 @@
+"""Single-kernel micro-benchmarks (CUDA-event timing) for the kernels of this package.
+
+  python -m ksanadit_b200.microbench gemm  --M 75600 --N 15360 --K 5120
+  python -m ksanadit_b200.microbench attn  --L 75600 --H 40 [--density 0.25]
+  python -m ksanadit_b200.microbench quant --M 75600 --K 5120
+  python -m ksanadit_b200.microbench prepass --L 75600 --H 40
+
+Each line reports the median device time of `--iters` launches after `--warmup` and the achieved
+TFLOP/s (contractions) or GB/s of algorithmic bytes (HBM-bound passes).  Used for profiler captures of
+one kernel on a small case as well.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+import torch
+
+from . import _lib, ops, radial_mask
+
+
+def timeit(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in ev:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in ev)
+    return ts[len(ts) // 2]
+
+
+def fp8_rand(*shape, scale=50.0):
+    return (torch.randn(*shape, device="cuda") * scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+
+
+def run_gemm(a):
+    M, N, K = a.M, a.N, a.K
+    xq, wq = fp8_rand(M, K), fp8_rand(N, K)
+    sx, sw = torch.rand(M, device="cuda") + 0.5, torch.rand(N, device="cuda") * 1e-4
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    epi = {"none": _lib.EPI_NONE, "gelu": _lib.EPI_GELU_TANH, "gate": _lib.EPI_GATE_RESIDUAL}[a.epilogue]
+    resid = torch.randn(M, N, device="cuda").to(torch.bfloat16) if epi == _lib.EPI_GATE_RESIDUAL else None
+    gate = torch.randn(1, N, device="cuda").to(torch.bfloat16) if epi == _lib.EPI_GATE_RESIDUAL else None
+    t = timeit(lambda: ops.fp8_gemm(xq, sx, wq, sw, bias, epilogue=epi, resid=resid, gate=gate, out=out), a.iters, a.warmup)
+    fl = 2.0 * M * N * K
+    print(f"fp8_gemm M={M} N={N} K={K} epilogue={a.epilogue}: {t:.3f} ms  {fl / t / 1e9:.1f} TFLOP/s")
+    if a.compare:
+        t2 = timeit(lambda: torch._scaled_mm(xq, wq.t(), scale_a=sx[:, None], scale_b=sw[None, :], bias=bias, out_dtype=torch.bfloat16),
+                    a.iters, a.warmup)
+        print(f"  torch._scaled_mm (row-wise scales, cuBLASLt): {t2:.3f} ms  {fl / t2 / 1e9:.1f} TFLOP/s")
+
+
+def run_attn(a):
+    L, H = a.L, a.H
+    q, k, v = (torch.randn(L, H, 128, device="cuda").to(torch.bfloat16) for _ in range(3))
+    km = ops.sage_kmean(k)
+    q8, qs = ops.sage_quant_int8(q, 128, premul=ops.q_premul(128))
+    k8, ks = ops.sage_quant_int8(k, 64, mean=km)
+    vt, vs = ops.sage_quant_v(v)
+    out = torch.empty(L, H, 128, dtype=torch.bfloat16, device="cuda")
+    offs = ents = None
+    pairs = ((L + 127) // 128) ** 2
+    if a.density < 1.0:
+        tpf = max(128, L // 21)
+        m = radial_mask.bernoulli_frame_tile_mask(L, tpf, seed=0)
+        o, e = radial_mask.compact_tile_lists(radial_mask.expand_to_kernel_granularity(m, 128))
+        offs, ents = torch.from_numpy(o).cuda(), torch.from_numpy(e).cuda()
+        pairs = int(e.size)
+        print(f"  tile mask density {m.mean():.3f}")
+    t = timeit(lambda: ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, tile_offsets=offs, tile_entries=ents, out=out), a.iters, a.warmup)
+    fl = 4.0 * H * 128 * 128 * 128 * pairs
+    print(f"sage_attn L={L} H={H} tiles/head={pairs}: {t:.3f} ms  {fl / t / 1e9:.1f} TFLOP/s (visited tiles)")
+    if a.compare and L <= 16384:
+        qq, kk, vv = (x.permute(1, 0, 2)[None] for x in (q, k, v))
+        t2 = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv), a.iters, a.warmup)
+        print(f"  torch SDPA bf16: {t2:.3f} ms  {4.0 * H * L * L * 128 / t2 / 1e9:.1f} TFLOP/s")
+
+
+def run_quant(a):
+    M, K = a.M, a.K
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    sh = torch.randn(1, K, device="cuda").to(torch.bfloat16)
+    w = torch.randn(K, device="cuda")
+    by = M * K * 3 + M * 4
+    for name, fn in (("quant_fp8_rowwise", lambda: ops.quant_fp8_rowwise(x)), ("adaln_quant_fp8", lambda: ops.adaln_quant_fp8(x, sh, sh)),
+                     ("layernorm_quant_fp8", lambda: ops.layernorm_quant_fp8(x, w, w))):
+        t = timeit(fn, a.iters, a.warmup)
+        print(f"{name} M={M} K={K}: {t:.3f} ms  {by / t / 1e6:.0f} GB/s")
+
+
+def run_prepass(a):
+    L, H = a.L, a.H
+    C = H * 128
+    qkv = torch.randn(L, 3 * C, device="cuda").to(torch.bfloat16)
+    w = torch.ones(C, device="cuda")
+    rope = ops.wan_rope_table(128, 1024)
+    grid = (21, max(1, L // 21 // 80), 80)
+    t3 = qkv.view(L, 3, H, 128)
+    km = torch.zeros(H, 128, device="cuda")
+    for name, fn, by in (
+        ("rmsnorm_rope_inplace(k, +mean)", lambda: ops.rmsnorm_rope_inplace(qkv[:, C:2 * C], w, 1e-6, rope, grid, want_mean=True), L * C * 4),
+        ("sage_quant_int8(q)", lambda: ops.sage_quant_int8(t3[:, 0], 128, premul=0.1), L * C * 3),
+        ("sage_quant_int8(k)", lambda: ops.sage_quant_int8(t3[:, 1], 64, mean=km), L * C * 3),
+        ("sage_quant_v", lambda: ops.sage_quant_v(t3[:, 2]), L * C * 5),
+        ("sage_kmean", lambda: ops.sage_kmean(t3[:, 1]), L * C * 2),
+    ):
+        t = timeit(fn, a.iters, a.warmup)
+        print(f"{name} L={L} H={H}: {t:.3f} ms  {by / t / 1e6:.0f} GB/s")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kind", choices=["gemm", "attn", "quant", "prepass"])
+    ap.add_argument("--M", type=int, default=75600)
+    ap.add_argument("--N", type=int, default=5120)
+    ap.add_argument("--K", type=int, default=5120)
+    ap.add_argument("--L", type=int, default=75600)
+    ap.add_argument("--H", type=int, default=40)
+    ap.add_argument("--density", type=float, default=1.0)
+    ap.add_argument("--epilogue", default="none", choices=["none", "gelu", "gate"])
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--compare", action="store_true", help="also time the library kernel for the same shape")
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    {"gemm": run_gemm, "attn": run_attn, "quant": run_quant, "prepass": run_prepass}[a.kind](a)
+    _lib.assert_device_ok()
+
+
+if __name__ == "__main__":
+    main()
+_ = np
