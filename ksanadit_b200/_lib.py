@@ -10,7 +10,7 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libksana_b200.so")
+LIB_PATH = os.environ.get("KSANA_B200_LIB", os.path.join(_HERE, "lib", "libksana_b200.so"))
 
 BF16, FP16 = 0, 1
 EPI_NONE, EPI_GELU_TANH, EPI_GATE_RESIDUAL = 0, 1, 2

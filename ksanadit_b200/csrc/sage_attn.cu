@@ -131,8 +131,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int s = 0; s < KST; ++s) { mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1); }
     for (int s = 0; s < VST; ++s) { mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1); }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 128);
-    mbar_init(p_full, 128);
+    mbar_init(s_empty, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
+    mbar_init(p_full, 4);
     mbar_init(p_empty, 1);
     fence_barrier_init();
   }
@@ -241,7 +241,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
     tmem_wait_st();
     tc_fence_before();
-    mbar_arrive(s_empty);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_empty);
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
       const Work w = get_work(p, idx);
       const int qrow = w.qt * BQ + row;
@@ -282,7 +283,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(s_empty);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty);
         if (!full) {
           // masked columns (ragged tail or dropped 64-token half) become -inf: never the maximum, P = 0
 #pragma unroll
@@ -350,7 +352,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tmem_wait_st();
         }
         tc_fence_before();
-        mbar_arrive(p_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
         ++g;
       }
       if (!ok) break;
