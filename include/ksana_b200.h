@@ -135,6 +135,22 @@ int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t 
 int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
                          int64_t head_stride, float* amax, void* vt, float* vs, ksb_stream_t stream);
 
+/* Allocation-free form of the V quantiser above: same inputs, same outputs (bit for bit), but the absmax
+ * scratch is a fixed array inside the library instead of a buffer from the caller.  It has no counterpart
+ * in KsanaDiT; it exists for callers that may not allocate device memory at the point of the call -- a host
+ * runtime that handed the library raw pointers out of an arena it sized in advance and keeps no allocator
+ * the library could use, or a latency-critical loop that must not reach cudaMalloc (which can stall on a
+ * device-wide synchronisation or fail when the arena owner has left no free memory).  Nothing is allocated
+ * or freed here, by the CUDA runtime or by any library.
+ *   - limit: H * D <= 65536 (at most 512 heads of 128); larger shapes are rejected with an error text
+ *   - the array costs 256 KB of device memory on every GPU that loads the library, until the process exits
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before starting any stream capture
+ *   - every call uses the same array: it is cleared at the start of each call, and two calls that overlap
+ *     on the GPU (different streams, or different host threads) race on it -- serialise them */
+int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                                 int64_t head_stride, void* vt, float* vs, ksb_stream_t stream);
+
 /* Sage-style attention core: INT8 Q.K^T (s32 accumulate) -> fp32 online softmax in the exp2 domain ->
  * e4m3 P -> FP8 P.V (f32 accumulate) on tcgen05, dense or block-sparse.
  * Replaces `sageattn(q, k, v, tensor_layout="NHD")` (sage_attn.py:75-81) and

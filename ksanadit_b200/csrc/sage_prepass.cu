@@ -280,6 +280,34 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
   }
 }
 
+// ---------------------------------------------------------------------------------- built-in scratch
+// Scratch of the allocation-free V quantiser entry point: per-(head, channel) absmax words.  It lives in
+// the library image, so every GPU that loads the library holds these 256 KB until the process exits.
+constexpr int64_t NOALLOC_MAX_HD = 65536;  // heads * 128 <= 65536, i.e. at most 512 heads
+static __device__ __align__(256) float g_v_amax_scratch[NOALLOC_MAX_HD];
+
+// In host code the array's name is only a handle: the device address has to be asked for, once per device,
+// with that device current.  Returns nullptr (with the error text set) if the runtime refuses.
+static float* v_amax_scratch_address() {
+  static float* cached[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    fail(KSB_ERR_CUDA, "cudaGetDevice failed or device index out of range: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_v_amax_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      fail(KSB_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch) failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
+
 int validate(const void* x, int dtype, int64_t L, int64_t H, int64_t Dh, int64_t ts, int64_t hs) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (Dh != D) return fail(KSB_ERR_UNSUPPORTED, "head size %lld is not supported (only 128)", (long long)Dh);
@@ -391,6 +419,19 @@ int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t
     prep::v_quant_transpose_kernel<__half><<<g2, prep::THREADS, 0, st>>>(static_cast<const __half*>(v), L, token_stride, head_stride, amax, static_cast<uint8_t*>(vt), vs, Lpad);
   }
   return check_launch("v quantiser");
+}
+
+int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                                 int64_t head_stride, void* vt, float* vs, ksb_stream_t stream) {
+  if (int rc = prep::validate(v, dtype, L, H, D, token_stride, head_stride)) return rc;
+  if (H * D > prep::NOALLOC_MAX_HD)
+    return fail(KSB_ERR_INVALID, "ksb_sage_quant_v_fp8_noalloc: heads * head_size = %lld exceeds the built-in scratch of %lld words; "
+                "use ksb_sage_quant_v_fp8 with caller-provided scratch", (long long)(H * D), (long long)prep::NOALLOC_MAX_HD);
+  float* amax = prep::v_amax_scratch_address();  // first call on a device resolves the address
+  if (!amax) return KSB_ERR_CUDA;
+  // same two passes as ksb_sage_quant_v_fp8; the absmax words are cleared first because the array keeps
+  // whatever the previous call left in it
+  return ksb_sage_quant_v_fp8(v, dtype, L, H, D, token_stride, head_stride, amax, vt, vs, stream);
 }
 
 }  // extern "C"
