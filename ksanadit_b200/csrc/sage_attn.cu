@@ -90,19 +90,53 @@ __device__ __forceinline__ float tree_max64(const uint32_t (&a)[32], const uint3
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
+#ifndef KSB_ATTN_POLY
+#define KSB_ATTN_POLY 0  // share of the exponentials evaluated on the FMA pipe: 0 = none, 1 = 1/4, 2 = 1/2
+#endif
+#ifdef KSB_ATTN_TIMING
+// development instrumentation: cycles spent by softmax warp 4 of every CTA in each phase of the tile loop
+__device__ unsigned long long g_attn_phase_cycles[16];
+#define KSB_T(i)                                                   \
+  do {                                                             \
+    const long long now_ = clock64();                              \
+    ph_[i] += now_ - tprev_;                                       \
+    tprev_ = now_;                                                 \
+  } while (0)
+#else
+#define KSB_T(i)
+#endif
+
+// 2^x for two values on the FMA / ALU pipes instead of the special-function unit: x = n + r with n the
+// nearest integer (taken from the low mantissa bits of x + 1.5 * 2^23) and r in [-0.5, 0.5]; 2^r by a
+// cubic (relative error < 8e-5, far below the e4m3 rounding step), n added to the exponent field.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 r = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+  float2 q = __ffma2_rn(r, make_float2(0.05508868396282196f, 0.05508868396282196f), make_float2(0.24260404706001282f, 0.24260404706001282f));
+  q = __ffma2_rn(q, r, make_float2(0.6932762265205383f, 0.6932762265205383f));
+  q = __ffma2_rn(q, r, make_float2(0.9999289512634277f, 0.9999289512634277f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23)));
+}
+
 // P = exp2(f * sc + c) for one 32-score chunk (f = 12582912 + S as fp32) -> 8 words of packed e4m3; the
 // exact (unrounded) values are added into four independent packed accumulators.  A masked score holds -inf
-// and yields exactly 0.
+// and yields 0 (or 2^-126, which rounds to 0 and vanishes in the row sum).
 __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], float sc, float c, uint32_t* pk, float2 (&acc)[4]) {
   const float2 sc2 = make_float2(sc, sc), c2 = make_float2(c, c);
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
     const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, c2);
     const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc2, c2);
-    const float e0 = fast_exp2(x01.x), e1 = fast_exp2(x01.y), e2 = fast_exp2(x23.x), e3 = fast_exp2(x23.y);
-    acc[(i >> 2) & 3] = __fadd2_rn(acc[(i >> 2) & 3], make_float2(e0, e1));
-    acc[((i >> 2) + 2) & 3] = __fadd2_rn(acc[((i >> 2) + 2) & 3], make_float2(e2, e3));
-    pk[i >> 2] = cvt_e4m3x4(e0, e1, e2, e3);
+    const float2 e01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+    const bool poly = (KSB_ATTN_POLY == 2) || (KSB_ATTN_POLY == 1 && ((i >> 2) & 1));
+    const float2 e23 = poly ? exp2_poly2(x23) : make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+    acc[(i >> 2) & 3] = __fadd2_rn(acc[(i >> 2) & 3], e01);
+    acc[((i >> 2) + 2) & 3] = __fadd2_rn(acc[((i >> 2) + 2) & 3], e23);
+    pk[i >> 2] = cvt_e4m3x4(e01.x, e01.y, e23.x, e23.y);
   }
 }
 
@@ -236,6 +270,10 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     T* out = static_cast<T*>(p.out);
     uint32_t g = 0;
     bool ok = true;
+#ifdef KSB_ATTN_TIMING
+    long long ph_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    long long tprev_ = clock64();
+#endif
     // pre-load the score accumulator for the first S = Q.K^T (completion #0 of s_empty)
 #pragma unroll
     for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
@@ -256,6 +294,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       const float qsc = p.qs[w.h * p.nq + w.qt];
       float m_used = -INFINITY, l = 0.f;
+      KSB_T(9);
       // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
       int e_next = entry_at(w, 0);
       float ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)], ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
@@ -270,14 +309,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int t = e >> 2, halves = e & 3;
         const int valid = min(BKV, p.Lk - t * BKV);
         const bool full = (halves == 3) && (valid == BKV);
+        KSB_T(0);
         if (!mbar_wait_warp(s_full, g & 1, p.status, (KERNEL_ID << 16) | 9)) { ok = false; break; }
         tc_fence_after();
+        KSB_T(1);
         uint32_t s[4][32];
         tmem_ld32(tmem_s + lane_sel + 0, s[0]);
         tmem_ld32(tmem_s + lane_sel + 32, s[1]);
         tmem_ld32(tmem_s + lane_sel + 64, s[2]);
         tmem_ld32(tmem_s + lane_sel + 96, s[3]);
         tmem_wait_ld();
+        KSB_T(2);
         // pre-load the accumulator for the next S = Q.K^T, then hand it back to the MMA issuer
 #pragma unroll
         for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
@@ -285,6 +327,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_empty);
+        KSB_T(3);
         if (!full) {
           // masked columns (ragged tail or dropped 64-token half) become -inf: never the maximum, P = 0
 #pragma unroll
@@ -309,6 +352,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           l *= alpha;
           m_used = m_new;
         }
+        KSB_T(4);
         // P = exp2(X - m_used + 8) -> e4m3, packed 4 per word; masked columns give exactly 0
         const float neg_m = (m_used == -INFINITY) ? 0.f : (P_SHIFT - m_used);
         uint32_t pk[32];
@@ -319,9 +363,11 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         exp_chunk(s[2], sc1, c1, pk + 16, acc);
         exp_chunk(s[3], sc1, c1, pk + 24, acc);
         l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+        KSB_T(5);
         // the previous P.V must have finished: it read the P buffer that is overwritten now and wrote the O
         // accumulator that is rescaled below
         if (!mbar_wait_warp(p_empty, (g & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
+        KSB_T(6);
         // row `row` of the K-major tile: eight 16-byte chunks, chunk index XORed with (row & 7)
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -329,6 +375,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           *reinterpret_cast<uint4*>(p_gen + row * 128 + ((c ^ (row & 7)) << 4)) = v4;
         }
         fence_proxy_async_smem();
+        KSB_T(7);
         if (rescale && j > 0) {
           // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now)
           tc_fence_after();
@@ -354,6 +401,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full);
+        KSB_T(8);
         ++g;
       }
       if (!ok) break;
@@ -380,7 +428,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       tc_fence_before();
+      KSB_T(10);
     }
+#ifdef KSB_ATTN_TIMING
+    if (warp == 4 && lane == 0)
+      for (int i = 0; i < 12; ++i) atomicAdd(&g_attn_phase_cycles[i], (unsigned long long)ph_[i]);
+#endif
   }
 
   // ------------------------------------------------------------------ common exit
@@ -396,6 +449,18 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 }  // namespace ksb
 
 using namespace ksb;
+
+#ifdef KSB_ATTN_TIMING
+extern "C" int ksb_debug_attn_phase_cycles(unsigned long long* out16, int reset) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out16, ksb::attn::g_attn_phase_cycles, 16 * sizeof(unsigned long long)) != cudaSuccess) return -2;
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(ksb::attn::g_attn_phase_cycles, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
                              const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,
