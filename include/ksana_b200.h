@@ -123,14 +123,14 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
                              int64_t pos0, float* colsum_partial, float* colmean, ksb_stream_t stream);
 
 /* INT8 block quantiser: xf = float(x) - mean[h,d] (if mean) then * premul (if premul != 0);
- * scale[h,b] = absmax(block)/127 (1 if zero); q = clamp(rint(xf/scale), +-127).
+ * scale[h,b] = absmax(block)/127 (1 if zero); q = clamp(rint(xf * (127/absmax)), +-127).
  * out: [H, Lpad, D] int8 with Lpad = roundup(L,128), padding zero-filled; scale: [H, Lpad/block].
  * block is 128 (Q) or 64 (K). */
 int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
                         int64_t head_stride, int block, float premul, const float* mean, void* out,
                         float* scale, ksb_stream_t stream);
 
-/* V quantiser: vs[h,d] = absmax over tokens / 448 (1 if zero); vt[h,d,l] = e4m3(float(v)/vs), token
+/* V quantiser: vs[h,d] = absmax over tokens / 448 (1 if zero); vt[h,d,l] = e4m3(float(v) * (448/absmax)), token
  * axis contiguous and zero-padded to Lpad.  amax: fp32 scratch [H*D] (overwritten). */
 int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
                          int64_t head_stride, float* amax, void* vt, float* vs, ksb_stream_t stream);

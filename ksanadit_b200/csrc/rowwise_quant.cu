@@ -1,7 +1,8 @@
 // HBM-bound row kernels: per-token FP8 (e4m3) activation quantiser, alone or fused behind
-// LayerNorm + adaLN modulate / affine LayerNorm.  One CTA walks rows; a row is read once from HBM
-// with 2 x 128-bit loads per 16 elements, held in registers across the reductions, and written once
-// (16 e4m3 bytes per 128-bit store).  Algorithmic bytes per row: 2K (read) + K (write) + 4 (scale).
+// LayerNorm + adaLN modulate / affine LayerNorm.  A row is owned by 1, 2 or 4 warps (by its width), read
+// once from HBM with 2 x 128-bit loads per 16 elements, held in registers across the reductions, and
+// written once (16 e4m3 bytes per 128-bit store); a CTA of 4 warps keeps up to 4 rows in flight and many
+// CTAs share an SM.  Algorithmic bytes per row: 2K (read) + K (write) + 4 (scale).
 //
 // Rounding points follow the eager PyTorch sequence this replaces, so the FP8 bytes match it bit for
 // bit: s = amax/448 (fp32 divide), inv = half(1/s), q = e4m3(half(x * inv)).
@@ -12,9 +13,9 @@
 namespace ksb {
 namespace rq {
 
-constexpr int THREADS = 256;
-constexpr int CHUNK = 16;     // elements per thread-chunk
-constexpr int MAX_CHUNKS = 4;  // K <= THREADS * CHUNK * MAX_CHUNKS = 16384
+constexpr int THREADS = 128;   // 4 warps per CTA; a row is owned by 1, 2 or 4 of them
+constexpr int CHUNK = 16;      // elements per thread-chunk: two 128-bit loads, one 128-bit e4m3 store
+// chunks per thread (NC) is 4 or 8: K <= warps_per_row * 32 * 16 * NC
 
 enum Mode : int { PLAIN = 0, ADALN = 1, LN_AFFINE = 2, STATIC = 3 };
 
@@ -33,21 +34,7 @@ struct Params {
   float* qscale;
 };
 
-__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
-  v = is_max ? warp_max(v) : warp_sum(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  __syncthreads();
-  if (l == 0) red[w] = v;
-  __syncthreads();
-  float r = red[0];
-#pragma unroll
-  for (int i = 1; i < THREADS / 32; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
-  return r;
-}
-
-template <typename T> __device__ __forceinline__ void load16(const T* p, float (&f)[16]) {
-  const uint4 a = *reinterpret_cast<const uint4*>(p);
-  const uint4 b = *reinterpret_cast<const uint4*>(p + 8);
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& a, const uint4& b, float (&f)[16]) {
   const T* ta = reinterpret_cast<const T*>(&a);
   const T* tb = reinterpret_cast<const T*>(&b);
 #pragma unroll
@@ -56,8 +43,7 @@ template <typename T> __device__ __forceinline__ void load16(const T* p, float (
     f[8 + i] = HalfOps<T>::to_f(tb[i]);
   }
 }
-template <typename T> __device__ __forceinline__ void store16(T* p, const float (&f)[16]) {
-  uint4 a, b;
+template <typename T> __device__ __forceinline__ void pack16(const float (&f)[16], uint4& a, uint4& b) {
   T* ta = reinterpret_cast<T*>(&a);
   T* tb = reinterpret_cast<T*>(&b);
 #pragma unroll
@@ -65,66 +51,150 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const float 
     ta[i] = HalfOps<T>::from_f(f[i]);
     tb[i] = HalfOps<T>::from_f(f[8 + i]);
   }
-  *reinterpret_cast<uint4*>(p) = a;
-  *reinterpret_cast<uint4*>(p + 8) = b;
 }
 template <typename T> __device__ __forceinline__ float round_half(float v) { return HalfOps<T>::to_f(HalfOps<T>::from_f(v)); }
 
-template <typename T, int MODE> __global__ void __launch_bounds__(THREADS) rowwise_kernel(const Params p) {
-  __shared__ float red[THREADS / 32];
+// Reduction over the WPR warps that own one row.  `red` is [2][4] floats per CTA, double-buffered by `par`.
+template <int WPR, bool IS_MAX> __device__ __forceinline__ float row_reduce(float v, float* red, int par, int warp) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  if (WPR == 1) return v;
+  if ((threadIdx.x & 31) == 0) red[par * 4 + warp] = v;
+  __syncthreads();
+  const int g0 = (warp / WPR) * WPR;
+  float r = red[par * 4 + g0];
+#pragma unroll
+  for (int i = 1; i < WPR; ++i) r = IS_MAX ? fmaxf(r, red[par * 4 + g0 + i]) : r + red[par * 4 + g0 + i];
+  return r;
+}
+
+// Rows are kept in registers in their packed half form between the HBM read and the HBM write.  With a
+// broadcast modulation (mod_rows == 1) the shift and (1 + scale) vectors, or the affine weight and bias, are
+// staged once per CTA in shared memory.
+template <typename T, int MODE, int WPR, int MAX_CHUNKS>
+__global__ void __launch_bounds__(THREADS, 4) rowwise_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float red[3][2][4];
+  constexpr int RPC = 4 / WPR;          // rows per CTA per iteration
+  constexpr int GT = WPR * 32;          // threads per row
+  const int warp = threadIdx.x >> 5;
+  const int rg = warp / WPR;            // row slot of this warp
+  const int t = threadIdx.x - rg * GT;  // thread index inside the row group
   const int nchunks = static_cast<int>(p.K / CHUNK);
   const T* x = static_cast<const T*>(p.x);
-  for (int64_t row = blockIdx.x; row < p.M; row += gridDim.x) {
-    float v[MAX_CHUNKS][16];
+  const bool staged = (MODE == ADALN && p.mod_rows == 1) || MODE == LN_AFFINE;
+  // Staged vectors are stored as 16-byte units in unit-major order (unit u of chunk ch at index u * nchunks + ch),
+  // so that consecutive threads, which own consecutive chunks, read consecutive 16-byte units: no bank conflicts.
+  if (MODE == ADALN && staged) {
+    uint4* s_shift = reinterpret_cast<uint4*>(smem);       // [2][nchunks] units of 8 halves
+    uint4* s_tsc = s_shift + 2 * nchunks;
+    for (int i = threadIdx.x; i < 2 * nchunks; i += THREADS) {
+      const int ch = i >> 1, u = i & 1;
+      const uint4 sh = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.shift) + ch * CHUNK + u * 8);
+      uint4 sc = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.scale) + ch * CHUNK + u * 8);
+      T* st = reinterpret_cast<T*>(&sc);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) st[e] = HalfOps<T>::from_f(1.f + HalfOps<T>::to_f(st[e]));  // (1 + scale) in half
+      s_shift[u * nchunks + ch] = sh;
+      s_tsc[u * nchunks + ch] = sc;
+    }
+    __syncthreads();
+  }
+  if (MODE == LN_AFFINE) {
+    float4* s_w = reinterpret_cast<float4*>(smem);  // [4][nchunks] units of 4 floats
+    float4* s_b = s_w + 4 * nchunks;
+    for (int i = threadIdx.x; i < 4 * nchunks; i += THREADS) {
+      const int ch = i >> 2, u = i & 3;
+      s_w[u * nchunks + ch] = *reinterpret_cast<const float4*>(p.w + ch * CHUNK + u * 4);
+      s_b[u * nchunks + ch] = p.b ? *reinterpret_cast<const float4*>(p.b + ch * CHUNK + u * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncthreads();
+  }
+  int par = 0;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * RPC; base < p.M; base += static_cast<int64_t>(gridDim.x) * RPC, par ^= 1) {
+    const int64_t row = base + rg;
+    const bool live = row < p.M;
+    uint4 va[MAX_CHUNKS], vb[MAX_CHUNKS];
     const T* xr = x + row * p.ldx;
 #pragma unroll
     for (int c = 0; c < MAX_CHUNKS; ++c) {
-      const int ch = threadIdx.x + c * THREADS;
-      if (ch < nchunks) load16<T>(xr + ch * CHUNK, v[c]);
+      const int ch = t + c * GT;
+      if (live && ch < nchunks) {
+        va[c] = *reinterpret_cast<const uint4*>(xr + ch * CHUNK);
+        vb[c] = *reinterpret_cast<const uint4*>(xr + ch * CHUNK + 8);
+      } else {
+        va[c] = make_uint4(0, 0, 0, 0);
+        vb[c] = make_uint4(0, 0, 0, 0);
+      }
     }
     if (MODE == ADALN || MODE == LN_AFFINE) {
       float s = 0.f;
 #pragma unroll
-      for (int c = 0; c < MAX_CHUNKS; ++c)
-        if (threadIdx.x + c * THREADS < nchunks)
+      for (int c = 0; c < MAX_CHUNKS; ++c) {
+        float f[16];
+        unpack16<T>(va[c], vb[c], f);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) s += v[c][i];
-      const float mean = block_reduce(s, false, red) / static_cast<float>(p.K);
+        for (int i = 0; i < 16; ++i) s += f[i];
+      }
+      const float mean = row_reduce<WPR, false>(s, &red[0][0][0], par, warp) / static_cast<float>(p.K);
       float s2 = 0.f;
 #pragma unroll
-      for (int c = 0; c < MAX_CHUNKS; ++c)
-        if (threadIdx.x + c * THREADS < nchunks)
+      for (int c = 0; c < MAX_CHUNKS; ++c) {
+        if (t + c * GT < nchunks) {
+          float f[16];
+          unpack16<T>(va[c], vb[c], f);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float d = v[c][i] - mean;
+            const float d = f[i] - mean;
             s2 += d * d;
           }
-      const float var = block_reduce(s2, false, red) / static_cast<float>(p.K);
+        }
+      }
+      const float var = row_reduce<WPR, false>(s2, &red[1][0][0], par, warp) / static_cast<float>(p.K);
       const float rstd = rsqrtf(var + p.eps);
-      const int64_t mrow = (p.mod_rows == 1) ? 0 : row;
 #pragma unroll
       for (int c = 0; c < MAX_CHUNKS; ++c) {
-        const int ch = threadIdx.x + c * THREADS;
-        if (ch < nchunks) {
+        const int ch = t + c * GT;
+        if (live && ch < nchunks) {
+          float f[16];
+          unpack16<T>(va[c], vb[c], f);
           if (MODE == ADALN) {
-            float sh[16], sc[16];
-            load16<T>(static_cast<const T*>(p.shift) + mrow * p.K + ch * CHUNK, sh);
-            load16<T>(static_cast<const T*>(p.scale) + mrow * p.K + ch * CHUNK, sc);
+            float sh[16], ts[16];
+            if (staged) {
+              const uint4* s_shift = reinterpret_cast<const uint4*>(smem);
+              const uint4* s_tsc = s_shift + 2 * nchunks;
+              unpack16<T>(s_shift[ch], s_shift[nchunks + ch], sh);
+              unpack16<T>(s_tsc[ch], s_tsc[nchunks + ch], ts);
+            } else {
+              const T* gs = static_cast<const T*>(p.shift) + row * p.K + ch * CHUNK;
+              const T* gc = static_cast<const T*>(p.scale) + row * p.K + ch * CHUNK;
+              unpack16<T>(*reinterpret_cast<const uint4*>(gs), *reinterpret_cast<const uint4*>(gs + 8), sh);
+              unpack16<T>(*reinterpret_cast<const uint4*>(gc), *reinterpret_cast<const uint4*>(gc + 8), ts);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) ts[i] = round_half<T>(1.f + ts[i]);  // (1 + scale) in half
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float ln = round_half<T>((v[c][i] - mean) * rstd);  // F.layer_norm output in half
-              const float t = round_half<T>(1.f + sc[i]);               // (1 + scale) in half
-              v[c][i] = round_half<T>(fmaf(ln, t, sh[i]));              // addcmul, one rounding
+              const float ln = round_half<T>((f[i] - mean) * rstd);  // F.layer_norm output in half
+              f[i] = fmaf(ln, ts[i], sh[i]);                          // addcmul, rounded once by pack16
             }
           } else {
+            const float4* s_w = reinterpret_cast<const float4*>(smem);
+            const float4* s_b = s_w + 4 * nchunks;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float y = (v[c][i] - mean) * rstd * p.w[ch * CHUNK + i];
-              if (p.b) y += p.b[ch * CHUNK + i];
-              v[c][i] = round_half<T>(y);
+            for (int u = 0; u < 4; ++u) {
+              const float4 wv = s_w[u * nchunks + ch], bv = s_b[u * nchunks + ch];
+              f[4 * u + 0] = (f[4 * u + 0] - mean) * rstd * wv.x + bv.x;
+              f[4 * u + 1] = (f[4 * u + 1] - mean) * rstd * wv.y + bv.y;
+              f[4 * u + 2] = (f[4 * u + 2] - mean) * rstd * wv.z + bv.z;
+              f[4 * u + 3] = (f[4 * u + 3] - mean) * rstd * wv.w + bv.w;
             }
           }
-          if (p.h_out) store16<T>(static_cast<T*>(p.h_out) + row * p.K + ch * CHUNK, v[c]);
+          pack16<T>(f, va[c], vb[c]);
+          if (p.h_out) {
+            T* ho = static_cast<T*>(p.h_out) + row * p.K + ch * CHUNK;
+            *reinterpret_cast<uint4*>(ho) = va[c];
+            *reinterpret_cast<uint4*>(ho + 8) = vb[c];
+          }
         }
       }
     }
@@ -141,48 +211,74 @@ template <typename T, int MODE> __global__ void __launch_bounds__(THREADS) rowwi
     } else {
       float am = 0.f;
 #pragma unroll
-      for (int c = 0; c < MAX_CHUNKS; ++c)
-        if (threadIdx.x + c * THREADS < nchunks)
+      for (int c = 0; c < MAX_CHUNKS; ++c) {
+        float f[16];
+        unpack16<T>(va[c], vb[c], f);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(v[c][i]));
-      am = block_reduce(am, true, red);
+        for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(f[i]));
+      }
+      am = row_reduce<WPR, true>(am, &red[2][0][0], par, warp);
       row_scale = (am > 0.f) ? __fdiv_rn(am, 448.f) : 1.f;
       inv_h = round_half<T>(__frcp_rn(row_scale));
     }
-    if (threadIdx.x == 0) p.qscale[row] = row_scale;
-    uint8_t* qr = p.q + row * p.K;
+    if (live) {
+      if (t == 0) p.qscale[row] = row_scale;
+      uint8_t* qr = p.q + row * p.K;
 #pragma unroll
-    for (int c = 0; c < MAX_CHUNKS; ++c) {
-      const int ch = threadIdx.x + c * THREADS;
-      if (ch < nchunks) {
-        float t[16];
+      for (int c = 0; c < MAX_CHUNKS; ++c) {
+        const int ch = t + c * GT;
+        if (ch < nchunks) {
+          float f[16];
+          unpack16<T>(va[c], vb[c], f);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) t[i] = round_half<T>(v[c][i] * inv_h);  // product formed in half precision
-        uint4 o;
-        o.x = cvt_e4m3x4(t[0], t[1], t[2], t[3]);
-        o.y = cvt_e4m3x4(t[4], t[5], t[6], t[7]);
-        o.z = cvt_e4m3x4(t[8], t[9], t[10], t[11]);
-        o.w = cvt_e4m3x4(t[12], t[13], t[14], t[15]);
-        *reinterpret_cast<uint4*>(qr + ch * CHUNK) = o;
+          for (int i = 0; i < 16; ++i) f[i] = round_half<T>(f[i] * inv_h);  // product formed in half precision
+          uint4 o;
+          o.x = cvt_e4m3x4(f[0], f[1], f[2], f[3]);
+          o.y = cvt_e4m3x4(f[4], f[5], f[6], f[7]);
+          o.z = cvt_e4m3x4(f[8], f[9], f[10], f[11]);
+          o.w = cvt_e4m3x4(f[12], f[13], f[14], f[15]);
+          *reinterpret_cast<uint4*>(qr + ch * CHUNK) = o;
+        }
       }
     }
   }
 }
 
+template <typename T, int MODE> int launch_t(const Params& p, cudaStream_t st) {
+  size_t smem = 0;
+  if (MODE == ADALN && p.mod_rows == 1) smem = 2 * p.K * sizeof(T);
+  if (MODE == LN_AFFINE) smem = 2 * p.K * sizeof(float);
+  // narrow rows: 1 or 2 warps per row and 4 chunks per thread; wide rows: all 4 warps on one row
+  const int wpr = p.K <= 2048 ? 1 : (p.K <= 4096 ? 2 : 4);
+  const bool wide = p.K > 8192;
+  const int rpc = 4 / wpr;
+  const int64_t want = (p.M + rpc - 1) / rpc;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+#define KSB_RQ_LAUNCH(W, NC)                                                                                                     \
+  do {                                                                                                                           \
+    if (smem > 48 * 1024 &&                                                                                                      \
+        cudaFuncSetAttribute(rowwise_kernel<T, MODE, W, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");                                                     \
+    rowwise_kernel<T, MODE, W, NC><<<grid, THREADS, smem, st>>>(p);                                                              \
+  } while (0)
+  if (wpr == 1) KSB_RQ_LAUNCH(1, 4);
+  else if (wpr == 2) KSB_RQ_LAUNCH(2, 4);
+  else if (!wide) KSB_RQ_LAUNCH(4, 4);
+  else KSB_RQ_LAUNCH(4, 8);
+#undef KSB_RQ_LAUNCH
+  return check_launch("rowwise quantiser");
+}
+
 template <int MODE> int launch(const Params& p, int dtype, cudaStream_t st) {
   if (p.M == 0) return 0;
-  const int64_t grid = p.M < (int64_t)sm_count() * 16 ? p.M : (int64_t)sm_count() * 16;
-  if (dtype == KSB_BF16)
-    rowwise_kernel<__nv_bfloat16, MODE><<<(unsigned)grid, THREADS, 0, st>>>(p);
-  else
-    rowwise_kernel<__half, MODE><<<(unsigned)grid, THREADS, 0, st>>>(p);
-  return check_launch("rowwise quantiser");
+  return dtype == KSB_BF16 ? launch_t<__nv_bfloat16, MODE>(p, st) : launch_t<__half, MODE>(p, st);
 }
 
 int validate(const Params& p, int dtype) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (p.M < 0 || p.K <= 0) return fail(KSB_ERR_INVALID, "bad shape M=%lld K=%lld", (long long)p.M, (long long)p.K);
-  if (p.K % CHUNK != 0 || p.K > (int64_t)THREADS * CHUNK * MAX_CHUNKS)
+  if (p.K % CHUNK != 0 || p.K > (int64_t)16384)
     return fail(KSB_ERR_INVALID, "K=%lld must be a multiple of 16 and <= 16384", (long long)p.K);
   if (p.ldx < p.K || p.ldx % 8 != 0) return fail(KSB_ERR_INVALID, "ldx=%lld must be >= K and a multiple of 8", (long long)p.ldx);
   if (p.M > 0 && (!p.x || !p.q || !p.qscale)) return fail(KSB_ERR_INVALID, "null pointer");
@@ -233,7 +329,7 @@ int ksb_layernorm_quant_fp8(const void* x, int dtype, int64_t M, int64_t K, int6
   p.x = x; p.M = M; p.K = K; p.ldx = ldx; p.w = w; p.b = b; p.eps = eps; p.mod_rows = 1;
   p.h_out = h_out; p.q = static_cast<uint8_t*>(q); p.qscale = qscale;
   if (int rc = rq::validate(p, dtype)) return rc;
-  if (!w) return fail(KSB_ERR_INVALID, "weight is null");
+  if (!w || !aligned16(w) || (b && !aligned16(b))) return fail(KSB_ERR_INVALID, "weight / bias null or not 16-byte aligned");
   return rq::launch<rq::LN_AFFINE>(p, dtype, static_cast<cudaStream_t>(stream));
 }
 

@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(THREADS) int8_block_quant_kernel(const T* __re
 #pragma unroll
   for (int i = 1; i < THREADS / 32; ++i) am = fmaxf(am, red[i]);
   const float sc = (am > 0.f) ? __fdiv_rn(am, 127.f) : 1.f;
+  const float inv = (am > 0.f) ? __fdiv_rn(127.f, am) : 1.f;
   if (threadIdx.x == 0) scale[(int64_t)h * (Lpad / BLOCK) + b] = sc;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) int8_block_quant_kernel(const T* __re
     uint32_t w[2] = {0, 0};
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      int q = __float2int_rn(__fdiv_rn(v[i][e], sc));
+      int q = __float2int_rn(__fmul_rn(v[i][e], inv));
       q = max(-127, min(127, q));
       w[e >> 2] |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e & 3));
     }
@@ -125,38 +126,43 @@ __global__ void __launch_bounds__(THREADS) int8_block_quant_kernel(const T* __re
 
 // ---------------------------------------------------------------------------------- V quantiser + transpose
 // grid (Lpad / 128, H): tile of 128 tokens x 128 channels -> vt[h][d][l0 .. l0+127] e4m3.
+// A thread quantises 4 consecutive tokens of 8 channels and writes one 32-bit word per channel into a
+// [channel][token] tile in shared memory whose 16-byte groups are XOR-swizzled by the channel group, so that
+// both the word writes and the 128-bit row reads are (almost) conflict free.
 template <typename T>
 __global__ void __launch_bounds__(THREADS) v_quant_transpose_kernel(const T* __restrict__ v, int64_t L, int64_t ts, int64_t hs,
                                                                      const float* __restrict__ amax, uint8_t* __restrict__ vt,
                                                                      float* __restrict__ vs, int64_t Lpad) {
-  __shared__ __align__(16) uint8_t tile[D][128 + 16];  // [d][token], padded rows
-  __shared__ float s_sc[D];
+  __shared__ __align__(16) uint32_t tile[D][32];  // [d][token / 4]
+  __shared__ float s_inv[D];
   const int h = blockIdx.y;
   const int64_t l0 = (int64_t)blockIdx.x * 128;
   if (threadIdx.x < D) {
     const float a = amax[h * D + threadIdx.x];
-    const float sc = (a > 0.f) ? __fdiv_rn(a, 448.f) : 1.f;
-    s_sc[threadIdx.x] = sc;
-    if (blockIdx.x == 0) vs[h * D + threadIdx.x] = sc;
+    s_inv[threadIdx.x] = (a > 0.f) ? __fdiv_rn(448.f, a) : 1.f;
+    if (blockIdx.x == 0) vs[h * D + threadIdx.x] = (a > 0.f) ? __fdiv_rn(a, 448.f) : 1.f;
   }
   __syncthreads();
+  const int cg = threadIdx.x & 15, tq0 = threadIdx.x >> 4;  // 16 channel groups x 16 token quads per pass
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int j = threadIdx.x + i * THREADS;
-    const int r = j >> 4, c = (j & 15) * 8;
-    const int64_t l = l0 + r;
-    float f[8];
-    if (l < L) {
-      load8<T>(v + l * ts + (int64_t)h * hs + c, f);
-    } else {
+  for (int pass = 0; pass < 2; ++pass) {
+    const int tq = tq0 + 16 * pass;
+    float f[4][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    for (int r = 0; r < 4; ++r) {
+      const int64_t l = l0 + tq * 4 + r;
+      if (l < L) {
+        load8<T>(v + l * ts + (int64_t)h * hs + cg * 8, f[r]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[r][e] = 0.f;
+      }
     }
 #pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-      const uint16_t pr = cvt_e4m3x2(__fdiv_rn(f[e], s_sc[c + e]), __fdiv_rn(f[e + 1], s_sc[c + e + 1]));
-      tile[c + e][r] = static_cast<uint8_t>(pr & 0xff);
-      tile[c + e + 1][r] = static_cast<uint8_t>(pr >> 8);
+    for (int e = 0; e < 8; ++e) {
+      const float inv = s_inv[cg * 8 + e];
+      const uint32_t w = cvt_e4m3x4(__fmul_rn(f[0][e], inv), __fmul_rn(f[1][e], inv), __fmul_rn(f[2][e], inv), __fmul_rn(f[3][e], inv));
+      tile[cg * 8 + e][tq ^ ((cg & 7) << 2)] = w;
     }
   }
   __syncthreads();
@@ -164,12 +170,11 @@ __global__ void __launch_bounds__(THREADS) v_quant_transpose_kernel(const T* __r
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int j = threadIdx.x + i * THREADS;
-    const int d = j >> 3, c = (j & 7) * 16;
-    const uint4 val = *reinterpret_cast<const uint4*>(&tile[d][c]);
-    *reinterpret_cast<uint4*>(vt + ((int64_t)h * D + d) * Lpad + l0 + c) = val;
+    const int d = j >> 3, c = j & 7;
+    const uint4 val = *reinterpret_cast<const uint4*>(&tile[d][(c ^ ((d >> 3) & 7)) << 2]);
+    *reinterpret_cast<uint4*>(vt + ((int64_t)h * D + d) * Lpad + l0 + c * 16) = val;
   }
 }
-
 
 // ---------------------------------------------------------------------------------- RMSNorm (+ RoPE) in place
 // Full-width RMSNorm over C = H*128 channels with an fp32 weight, optionally followed by the 3-axis
@@ -193,7 +198,7 @@ template <typename T, bool ROPE>
 __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
                                                                   const float* __restrict__ w, float eps, RopeGrid rg,
                                                                   float* __restrict__ colsum_partial) {
-  __shared__ float red[NR_THREADS / 32];
+  __shared__ float red[2][NR_THREADS / 32];
   const int nvec = C / 8;
   const int64_t l0 = (int64_t)blockIdx.x * NR_ROWS;
   const int64_t l1 = min(L, l0 + NR_ROWS);
@@ -202,26 +207,39 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
   for (int i = 0; i < NR_MAX_VEC; ++i)
 #pragma unroll
     for (int e = 0; e < 8; ++e) cs[i][e] = 0.f;
-  for (int64_t l = l0; l < l1; ++l) {
+  // the next row is fetched while the current one is reduced and written
+  uint4 cur[NR_MAX_VEC], nxt[NR_MAX_VEC];
+#pragma unroll
+  for (int i = 0; i < NR_MAX_VEC; ++i) {
+    const int j = threadIdx.x + i * NR_THREADS;
+    cur[i] = (j < nvec) ? *reinterpret_cast<const uint4*>(x + l0 * ld + j * 8) : make_uint4(0, 0, 0, 0);
+  }
+  int par = 0;
+  for (int64_t l = l0; l < l1; ++l, par ^= 1) {
     T* row = x + l * ld;
-    float v[NR_MAX_VEC][8];
+    if (l + 1 < l1) {
+#pragma unroll
+      for (int i = 0; i < NR_MAX_VEC; ++i) {
+        const int j = threadIdx.x + i * NR_THREADS;
+        nxt[i] = (j < nvec) ? *reinterpret_cast<const uint4*>(row + ld + j * 8) : make_uint4(0, 0, 0, 0);
+      }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < NR_MAX_VEC; ++i) {
-      const int j = threadIdx.x + i * NR_THREADS;
-      if (j < nvec) {
-        load8<T>(row + j * 8, v[i]);
+      const T* t = reinterpret_cast<const T*>(&cur[i]);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+      for (int e = 0; e < 8; ++e) {
+        const float f = HalfOps<T>::to_f(t[e]);
+        ss += f * f;
       }
     }
     ss = warp_sum(ss);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    if ((threadIdx.x & 31) == 0) red[par][threadIdx.x >> 5] = ss;
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < NR_THREADS / 32; ++i) tot += red[i];
+    for (int i = 0; i < NR_THREADS / 32; ++i) tot += red[par][i];
     const float rstd = rsqrtf(tot / (float)C + eps);
     int cf = 0, ch = 0, cw = 0;
     bool rotate = false;
@@ -240,10 +258,12 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
     for (int i = 0; i < NR_MAX_VEC; ++i) {
       const int j = threadIdx.x + i * NR_THREADS;
       if (j < nvec) {
+        const T* t = reinterpret_cast<const T*>(&cur[i]);
+        const float4 w0 = *reinterpret_cast<const float4*>(w + j * 8), w1 = *reinterpret_cast<const float4*>(w + j * 8 + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         float y[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(v[i][e] * rstd * w[j * 8 + e]));
+        for (int e = 0; e < 8; ++e) y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(HalfOps<T>::to_f(t[e]) * rstd * wv[e]));
         if (ROPE && rotate) {
           const int p0 = ((j * 8) & (D - 1)) >> 1;  // first rotation pair of this vector inside its head
 #pragma unroll
@@ -266,6 +286,8 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
         *reinterpret_cast<uint4*>(row + j * 8) = o;
       }
     }
+#pragma unroll
+    for (int i = 0; i < NR_MAX_VEC; ++i) cur[i] = nxt[i];
   }
   if (colsum_partial) {
 #pragma unroll
@@ -356,7 +378,7 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
                              float* colsum_partial, float* colmean, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (L <= 0 || C <= 0 || C % 128 != 0 || C > 256 * 8 * prep::NR_MAX_VEC) return fail(KSB_ERR_INVALID, "C=%lld must be a multiple of 128 and <= 8192", (long long)C);
-  if (!x || !w || !aligned16(x) || ld < C || ld % 8 != 0) return fail(KSB_ERR_INVALID, "x/w null, unaligned or bad row stride");
+  if (!x || !w || !aligned16(x) || !aligned16(w) || ld < C || ld % 8 != 0) return fail(KSB_ERR_INVALID, "x/w null, unaligned or bad row stride");
   if ((colsum_partial == nullptr) != (colmean == nullptr)) return fail(KSB_ERR_INVALID, "colsum_partial and colmean go together");
   if (colsum_partial && !aligned16(colsum_partial)) return fail(KSB_ERR_INVALID, "colsum_partial must be 16-byte aligned");
   prep::RopeGrid rg{};

@@ -133,7 +133,8 @@ def int8_block_quant(x: torch.Tensor, block: int, premul: float | None = None, m
 
     x: [L, H, D] bf16/fp16.  xf = float(x) (- mean[h,d]) (* premul), all fp32.
     scale[h,b] = absmax over the block's (tokens x D) / 127 (1.0 if the block is zero);
-    q = clamp(round_half_even(xf / scale), -127, 127).
+    q = clamp(round_half_even(xf * inv), -127, 127) with inv = 127 / absmax (1.0 if zero) -- one
+    fp32 divide per block, one multiply per element.
     Returns (q8 [H, Lpad, D] int8 zero-padded to a multiple of 128 tokens,
              scale [H, Lpad // block] fp32 with 1.0 in fully padded blocks).
     """
@@ -150,7 +151,8 @@ def int8_block_quant(x: torch.Tensor, block: int, premul: float | None = None, m
     xb = xp.view(nb, block, H, D)
     amax = xb.abs().amax(dim=(1, 3))  # [nb, H]
     scale = torch.where(amax > 0, _div(amax, INT8_MAX), torch.ones_like(amax))
-    q = torch.round(xb / scale[:, None, :, None]).clamp_(-INT8_MAX, INT8_MAX).to(torch.int8)
+    inv = torch.where(amax > 0, torch.full_like(amax, INT8_MAX) / amax, torch.ones_like(amax))
+    q = torch.round(xb * inv[:, None, :, None]).clamp_(-INT8_MAX, INT8_MAX).to(torch.int8)
     q8 = q.view(Lpad, H, D).permute(1, 0, 2).contiguous()
     return q8, scale.t().contiguous()
 
@@ -158,7 +160,8 @@ def int8_block_quant(x: torch.Tensor, block: int, premul: float | None = None, m
 def v_quant_fp8(v: torch.Tensor):
     """Per-(head, channel) e4m3 quantisation of V with the token axis made contiguous.
 
-    v: [L,H,D].  s[h,d] = absmax over tokens / 448 (1.0 if zero); v8 = (float(v) / s).to(e4m3).
+    v: [L,H,D].  s[h,d] = absmax over tokens / 448 (1.0 if zero); v8 = (float(v) * inv).to(e4m3) with
+    inv = 448 / absmax (1.0 if zero), saturated at +-448.
     Returns (vt8 [H, D, Lpad] e4m3, zero padded to a multiple of 128 tokens; s [H, D] fp32).
     (Shape follows sage_sla.py:222-228: transpose + pad + per-(b,h,d) scale.)
     """
@@ -166,7 +169,8 @@ def v_quant_fp8(v: torch.Tensor):
     vf = v.float()
     amax = vf.abs().amax(dim=0)  # [H, D]
     s = torch.where(amax > 0, _div(amax, E4M3_MAX), torch.ones_like(amax))
-    v8 = (vf / s[None]).to(torch.float8_e4m3fn)
+    inv = torch.where(amax > 0, torch.full_like(amax, E4M3_MAX) / amax, torch.ones_like(amax))
+    v8 = (vf * inv[None]).clamp_(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
     Lpad = (L + KV_TILE - 1) // KV_TILE * KV_TILE
     out = torch.zeros(H, D, Lpad, dtype=torch.uint8)
     out[:, :, :L] = v8.view(torch.uint8).permute(1, 2, 0)
