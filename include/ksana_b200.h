@@ -65,12 +65,14 @@ int ksb_quant_fp8_static(const void* x, int dtype, int64_t M, int64_t K, int64_t
  * Replaces `torch.addcmul(shift, LayerNorm(x), 1 + scale)` (ksana/models/wan/wan_model.py:374,391;
  * ksana/operations/ops.py:41-52) followed by the quantiser above.
  *   h = shift + LN(x) * (1 + scale), LN without affine, eps; computed in fp32, rounded to half at the
- *   points the eager path rounds (after LN, after 1+scale, after the addcmul).
+ *   points the eager path rounds: after LN, after 1+scale, after the addcmul (round_product == 0, Wan), or
+ *   additionally after the product for `LN(x) * (1 + scale) + shift` written as two eager ops
+ *   (round_product == 1, Qwen-Image: ksana/models/qwen/transformer.py:171-194).
  * shift/scale: [mod_rows, K] half with mod_rows == 1 (broadcast) or M.  h_out (optional, may be NULL)
  * receives h in half precision.  K % 16 == 0, K <= 16384. */
 int ksb_adaln_quant_fp8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const void* shift,
-                        const void* scale, int64_t mod_rows, float eps, void* h_out, void* q, float* qscale,
-                        ksb_stream_t stream);
+                        const void* scale, int64_t mod_rows, int round_product, float eps, void* h_out, void* q,
+                        float* qscale, ksb_stream_t stream);
 
 /* Affine fp32 LayerNorm fused with the per-token FP8 quantiser (Wan norm3 before cross-attention,
  * wan_model.py:296-302,390; ops.py:45-50).  w, b: fp32 [K] (b may be NULL). */
@@ -107,20 +109,27 @@ int64_t ksb_sage_kmean_scratch_floats(int64_t L, int64_t H, int64_t D);
 int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
                    int64_t head_stride, float* partial, float* km, ksb_stream_t stream);
 
-/* Full-width RMSNorm with an fp32 weight, optionally followed by the 3-axis rotary embedding, in place
- * on a [L, C] half view (row stride ld; e.g. the Q or K third of a fused QKV output), C = heads * 128.
- * Replaces norm_q / norm_k (`x.float() * rsqrt(mean(x^2) + eps) * w`, ksana/operations/ops.py:64-70 via
- * ksana/models/wan/wan_model.py:81-90,164-165) and apply_default_rope (ksana/utils/rope.py:62-128).
- * rope_table: fp32 [table_len][64][2] = (cos, sin) of the reference's concatenated axis tables
- * (wan_model.py:676-684); rotation pair p of a head reads axis f for p < nf, h for p < nf + nh, else w;
- * row l sits at global position pos0 + l of an F x Hh x Ww grid, rows past the grid are not rotated.
+/* RMSNorm with an fp32 weight, optionally followed by the 3-axis rotary embedding, in place on a [L, C]
+ * half view (row stride ld; e.g. the Q or K third of a fused QKV output), C = heads * 128.
+ * per_head == 0: normalise over all C channels, w is [C]  (Wan: norm_q / norm_k,
+ *   `x.float() * rsqrt(mean(x^2) + eps) * w`, ksana/operations/ops.py:64-70 via
+ *   ksana/models/wan/wan_model.py:81-90,164-165);
+ * per_head == 1: normalise each head's 128 channels, w is [128]  (Qwen-Image: norm_q / norm_k /
+ *   norm_added_q / norm_added_k, ksana/models/qwen/attention.py:267-272,340-343).
+ * Rotation (apply_default_rope, ksana/utils/rope.py:62-128; apply_rotary_emb_qwen, qwen/attention.py:31-59):
+ * rope_table is fp32 [table_len][64][2] = (cos, sin); rotation pair p of a head reads table row `coord` with
+ * coord = the token's frame index for p < nf, its row index for p < nf + nh, else its column index; row l sits
+ * at position pos0 + l of an F x Hh x Ww grid (rows past the grid are not rotated).  The caller puts whatever
+ * angle belongs to coordinate index r of each axis into row r (Wan: r * inv_freq; Qwen: centred positions).
+ * diag == 1 (grid (F,1,1)): the running position drives all three axes (Qwen text tokens).
  * rope_table NULL = no rotation.  colsum_partial (fp32 scratch, ksb_rmsnorm_rope_scratch_floats) with
- * colmean [C]: also returns the per-channel mean over the L rows of the values written (the K
- * smoothing vector, sage_sla.py:198); both NULL to skip. */
+ * colmean [C]: also returns the per-channel mean over the L rows of the values written (the K smoothing
+ * vector, sage_sla.py:198); both NULL to skip. */
 int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C);
-int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, float eps,
-                             const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww,
-                             int64_t pos0, float* colsum_partial, float* colmean, ksb_stream_t stream);
+int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, int per_head,
+                             float eps, const float* rope_table, int table_len, int nf, int nh, int F, int Hh,
+                             int Ww, int64_t pos0, int diag, float* colsum_partial, float* colmean,
+                             ksb_stream_t stream);
 
 /* INT8 block quantiser: xf = float(x) - mean[h,d] (if mean) then * premul (if premul != 0);
  * scale[h,b] = absmax(block)/127 (1 if zero); q = clamp(rint(xf * (127/absmax)), +-127).

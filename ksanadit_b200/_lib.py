@@ -23,7 +23,7 @@ SIGNATURES = {
     "ksb_sm_count": (c_int, []),
     "ksb_quant_fp8_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ksb_quant_fp8_static": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "ksb_adaln_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_float,
+    "ksb_adaln_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int, c_float,
                                     c_void_p, c_void_p, c_void_p, c_void_p]),
     "ksb_layernorm_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_float,
                                         c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -33,8 +33,8 @@ SIGNATURES = {
     "ksb_sage_kmean_scratch_floats": (c_int64, [c_int64, c_int64, c_int64]),
     "ksb_sage_kmean": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ksb_rmsnorm_rope_scratch_floats": (c_int64, [c_int64, c_int64]),
-    "ksb_rmsnorm_rope_inplace": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int, c_int,
-                                         c_int, c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "ksb_rmsnorm_rope_inplace": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_float, c_void_p, c_int,
+                                         c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "ksb_sage_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_void_p,
                                     c_void_p, c_void_p, c_void_p]),
     "ksb_sage_quant_v_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,

@@ -25,6 +25,7 @@ struct Params {
   const void* shift;  // ADALN
   const void* scale;  // ADALN
   int64_t mod_rows;
+  int round_product;  // ADALN: 0 = addcmul(shift, ln, 1+scale) (one rounding), 1 = ln * (1+scale) rounded, then + shift
   const float* w;  // LN_AFFINE
   const float* b;
   float eps;
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(THREADS, 4) rowwise_kernel(const Params p) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float ln = round_half<T>((f[i] - mean) * rstd);  // F.layer_norm output in half
-              f[i] = fmaf(ln, ts[i], sh[i]);                          // addcmul, rounded once by pack16
+              f[i] = p.round_product ? (round_half<T>(ln * ts[i]) + sh[i]) : fmaf(ln, ts[i], sh[i]);  // rounded once more by pack16
             }
           } else {
             const float4* s_w = reinterpret_cast<const float4*>(smem);
@@ -312,9 +313,10 @@ int ksb_quant_fp8_static(const void* x, int dtype, int64_t M, int64_t K, int64_t
 }
 
 int ksb_adaln_quant_fp8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, const void* shift,
-                        const void* scale, int64_t mod_rows, float eps, void* h_out, void* q, float* qscale,
-                        ksb_stream_t stream) {
+                        const void* scale, int64_t mod_rows, int round_product, float eps, void* h_out, void* q,
+                        float* qscale, ksb_stream_t stream) {
   rq::Params p{};
+  p.round_product = round_product ? 1 : 0;
   p.x = x; p.M = M; p.K = K; p.ldx = ldx; p.shift = shift; p.scale = scale; p.mod_rows = mod_rows; p.eps = eps;
   p.h_out = h_out; p.q = static_cast<uint8_t*>(q); p.qscale = qscale;
   if (int rc = rq::validate(p, dtype)) return rc;

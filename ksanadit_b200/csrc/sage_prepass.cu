@@ -192,9 +192,10 @@ struct RopeGrid {
   int table_len, nf, nh;
   int F, Hh, Ww;
   int64_t pos0;  // global index of row 0 (sequence-parallel shard offset)
+  int diag;      // 1: one running position drives all three axes (text tokens of the Qwen-Image block)
 };
 
-template <typename T, bool ROPE>
+template <typename T, bool ROPE, bool PER_HEAD>
 __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
                                                                   const float* __restrict__ w, float eps, RopeGrid rg,
                                                                   float* __restrict__ colsum_partial) {
@@ -234,13 +235,33 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
         ss += f * f;
       }
     }
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[par][threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
+    float rstd_v[NR_MAX_VEC];
+    if (PER_HEAD) {
+      // RMSNorm over each head's 128 channels: 16 consecutive 8-channel vectors, i.e. 16 consecutive lanes
 #pragma unroll
-    for (int i = 0; i < NR_THREADS / 32; ++i) tot += red[par][i];
-    const float rstd = rsqrtf(tot / (float)C + eps);
+      for (int i = 0; i < NR_MAX_VEC; ++i) {
+        const T* t = reinterpret_cast<const T*>(&cur[i]);
+        float hs = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float f = HalfOps<T>::to_f(t[e]);
+          hs += f * f;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
+        rstd_v[i] = rsqrtf(hs / (float)D + eps);
+      }
+    } else {
+      ss = warp_sum(ss);
+      if ((threadIdx.x & 31) == 0) red[par][threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR_THREADS / 32; ++i) tot += red[par][i];
+      const float r = rsqrtf(tot / (float)C + eps);
+#pragma unroll
+      for (int i = 0; i < NR_MAX_VEC; ++i) rstd_v[i] = r;
+    }
     int cf = 0, ch = 0, cw = 0;
     bool rotate = false;
     if (ROPE) {
@@ -252,6 +273,7 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
         const int rem = (int)(pos - (int64_t)cf * per_frame);
         ch = rem / rg.Ww;
         cw = rem - ch * rg.Ww;
+        if (rg.diag) ch = cw = cf;
       }
     }
 #pragma unroll
@@ -259,11 +281,12 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
       const int j = threadIdx.x + i * NR_THREADS;
       if (j < nvec) {
         const T* t = reinterpret_cast<const T*>(&cur[i]);
-        const float4 w0 = *reinterpret_cast<const float4*>(w + j * 8), w1 = *reinterpret_cast<const float4*>(w + j * 8 + 4);
+        const int wofs = PER_HEAD ? ((j * 8) & (D - 1)) : j * 8;
+        const float4 w0 = *reinterpret_cast<const float4*>(w + wofs), w1 = *reinterpret_cast<const float4*>(w + wofs + 4);
         const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         float y[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(HalfOps<T>::to_f(t[e]) * rstd * wv[e]));
+        for (int e = 0; e < 8; ++e) y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(HalfOps<T>::to_f(t[e]) * rstd_v[i] * wv[e]));
         if (ROPE && rotate) {
           const int p0 = ((j * 8) & (D - 1)) >> 1;  // first rotation pair of this vector inside its head
 #pragma unroll
@@ -373,9 +396,9 @@ int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C) {
   return ((L + prep::NR_ROWS - 1) / prep::NR_ROWS) * C;
 }
 
-int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, float eps,
+int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, int per_head, float eps,
                              const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
-                             float* colsum_partial, float* colmean, ksb_stream_t stream) {
+                             int diag, float* colsum_partial, float* colmean, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (L <= 0 || C <= 0 || C % 128 != 0 || C > 256 * 8 * prep::NR_MAX_VEC) return fail(KSB_ERR_INVALID, "C=%lld must be a multiple of 128 and <= 8192", (long long)C);
   if (!x || !w || !aligned16(x) || !aligned16(w) || ld < C || ld % 8 != 0) return fail(KSB_ERR_INVALID, "x/w null, unaligned or bad row stride");
@@ -384,15 +407,21 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
   prep::RopeGrid rg{};
   if (rope_table) {
     if (nf < 0 || nh < 0 || nf + nh > 64 || F <= 0 || Hh <= 0 || Ww <= 0) return fail(KSB_ERR_INVALID, "bad rope grid");
-    if (F > table_len || Hh > table_len || Ww > table_len) return fail(KSB_ERR_INVALID, "rope table too short for the grid");
+    if (F > table_len || (!diag && (Hh > table_len || Ww > table_len))) return fail(KSB_ERR_INVALID, "rope table too short for the grid");
+    if (diag && (Hh != 1 || Ww != 1)) return fail(KSB_ERR_INVALID, "diag positions need a grid of (F, 1, 1)");
     rg.table = reinterpret_cast<const float2*>(rope_table); rg.table_len = table_len; rg.nf = nf; rg.nh = nh;
-    rg.F = F; rg.Hh = Hh; rg.Ww = Ww; rg.pos0 = pos0;
+    rg.F = F; rg.Hh = Hh; rg.Ww = Ww; rg.pos0 = pos0; rg.diag = diag ? 1 : 0;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int blocks = (int)((L + prep::NR_ROWS - 1) / prep::NR_ROWS);
-#define KSB_LAUNCH_NR(T, R) prep::rmsnorm_rope_kernel<T, R><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg, colsum_partial)
-  if (dtype == KSB_BF16) { if (rope_table) KSB_LAUNCH_NR(__nv_bfloat16, true); else KSB_LAUNCH_NR(__nv_bfloat16, false); }
-  else { if (rope_table) KSB_LAUNCH_NR(__half, true); else KSB_LAUNCH_NR(__half, false); }
+#define KSB_LAUNCH_NR(T, R, P) prep::rmsnorm_rope_kernel<T, R, P><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg, colsum_partial)
+#define KSB_LAUNCH_NR2(T)                                                          \
+  do {                                                                             \
+    if (rope_table) { if (per_head) KSB_LAUNCH_NR(T, true, true); else KSB_LAUNCH_NR(T, true, false); } \
+    else { if (per_head) KSB_LAUNCH_NR(T, false, true); else KSB_LAUNCH_NR(T, false, false); }           \
+  } while (0)
+  if (dtype == KSB_BF16) KSB_LAUNCH_NR2(__nv_bfloat16); else KSB_LAUNCH_NR2(__half);
+#undef KSB_LAUNCH_NR2
 #undef KSB_LAUNCH_NR
   if (int rc = check_launch("rmsnorm/rope")) return rc;
   if (colsum_partial) {

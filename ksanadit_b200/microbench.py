@@ -4,6 +4,7 @@
   python -m ksanadit_b200.microbench attn  --L 75600 --H 40 [--density 0.25]
   python -m ksanadit_b200.microbench quant --M 75600 --K 5120
   python -m ksanadit_b200.microbench prepass --L 75600 --H 40
+  python -m ksanadit_b200.microbench qwen [--layers 60]
 
 Each line reports the median device time of `--iters` launches after `--warmup` and the achieved
 TFLOP/s (contractions) or GB/s of algorithmic bytes (HBM-bound passes).  Used for profiler captures of
@@ -114,9 +115,34 @@ def run_prepass(a):
         print(f"{name} L={L} H={H}: {t:.3f} ms  {by / t / 1e6:.0f} GB/s")
 
 
+def run_qwen(a):
+    """Qwen-Image-20B-shaped MMDiT step: 60 dual-stream blocks, dim 3072, 24 heads, 6889 image + 256 text tokens."""
+    from .qwen_block import B200QwenBlock
+    dim, heads, ffn, grid, Lt = 3072, 24, 12288, (1, 83, 83), 256
+    layers = a.layers
+    blocks = [B200QwenBlock(dim, heads, ffn).random_init(100 + i) for i in range(layers)]
+    Li = grid[1] * grid[2]
+    img = torch.randn(1, Li, dim, device="cuda").to(torch.bfloat16)
+    txt = torch.randn(1, Lt, dim, device="cuda").to(torch.bfloat16)
+    temb = torch.randn(1, dim, device="cuda").to(torch.bfloat16)
+
+    def step():
+        t, i = txt, img
+        with torch.no_grad():
+            for b in blocks:
+                t, i = b(i, t, temb, img_grid=grid)
+        return i
+
+    t = timeit(step, a.iters, a.warmup)
+    L = Li + Lt
+    fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
+    print(f"qwen-image step: {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s ({fl / 1e15:.4f} PFLOP)")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemm", "attn", "quant", "prepass"])
+    ap.add_argument("kind", choices=["gemm", "attn", "quant", "prepass", "qwen"])
+    ap.add_argument("--layers", type=int, default=60)
     ap.add_argument("--M", type=int, default=75600)
     ap.add_argument("--N", type=int, default=5120)
     ap.add_argument("--K", type=int, default=5120)
@@ -130,7 +156,7 @@ def main():
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
-    {"gemm": run_gemm, "attn": run_attn, "quant": run_quant, "prepass": run_prepass}[a.kind](a)
+    {"gemm": run_gemm, "attn": run_attn, "quant": run_quant, "prepass": run_prepass, "qwen": run_qwen}[a.kind](a)
     _lib.assert_device_ok()
 
 

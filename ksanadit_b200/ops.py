@@ -102,8 +102,9 @@ def quant_fp8_static(x: torch.Tensor, scale_input: torch.Tensor | None):
     return q, s
 
 
-def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False):
-    """h = shift + LN(x)*(1+scale) -> per-token FP8.  x [M,K]; shift/scale [1,K] or [M,K]."""
+def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False, round_product=False):
+    """h = shift + LN(x)*(1+scale) -> per-token FP8.  x [M,K]; shift/scale [1,K] or [M,K].
+    round_product: round LN(x)*(1+scale) to half before adding shift (the Qwen-Image block's eager order)."""
     _cuda(x, shift, scale)
     M, K = x.shape
     shift = shift.reshape(-1, K).contiguous()
@@ -113,7 +114,7 @@ def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False):
     s = torch.empty(M, dtype=torch.float32, device=x.device)
     h = torch.empty(M, K, dtype=x.dtype, device=x.device) if want_h else None
     _lib.check(_lib.load().ksb_adaln_quant_fp8(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(shift), _p(scale),
-                                               shift.shape[0], float(eps), _p(h), _p(q), _p(s), _stream()),
+                                               shift.shape[0], int(round_product), float(eps), _p(h), _p(q), _p(s), _stream()),
                "ksb_adaln_quant_fp8")
     STATS.count(1)
     return (q, s, h) if want_h else (q, s)
@@ -275,15 +276,17 @@ def wan_rope_table(head_dim: int = 128, max_len: int = 1024, theta: float = 1000
     return _ROPE_TABLES[key]
 
 
-def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean=False):
+def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean=False, per_head=False, diag=False):
     """x: [L, C] half view (row stride allowed), normalised (and rotated) in place.
 
-    rope: result of wan_rope_table or None; grid: (F, H, W).  Returns the fp32 column mean [C] of the
-    written values when want_mean.
+    w: fp32 [C] (norm over all channels) or [128] with per_head (norm over each head's 128 channels).
+    rope: (table [len,64,2] fp32, n_f, n_h) or None; grid: (F, H, W); diag: one position for all axes.
+    Returns the fp32 column mean [C] of the written values when want_mean.
     """
     _cuda(x, w)
     assert x.dim() == 2 and x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous()
     L, C = x.shape
+    assert w.numel() == (128 if per_head else C)
     lib = _lib.load()
     partial = mean = None
     if want_mean:
@@ -294,7 +297,36 @@ def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean
         tab, nf, nh = rope
         tlen = tab.shape[0]
         F, Hh, Ww = (int(v) for v in grid)
-    _lib.check(lib.ksb_rmsnorm_rope_inplace(_p(x), _dt(x), L, C, x.stride(0) if L > 1 else C, _p(w), float(eps), _p(tab), tlen, nf, nh,
-                                            F, Hh, Ww, int(pos0), _p(partial), _p(mean), _stream()), "ksb_rmsnorm_rope_inplace")
+    _lib.check(lib.ksb_rmsnorm_rope_inplace(_p(x), _dt(x), L, C, x.stride(0) if L > 1 else C, _p(w), int(per_head), float(eps), _p(tab),
+                                            tlen, nf, nh, F, Hh, Ww, int(pos0), int(diag), _p(partial), _p(mean), _stream()),
+               "ksb_rmsnorm_rope_inplace")
     STATS.count(2 if want_mean else 1)
     return mean
+
+
+def qwen_rope_tables(img_grid, txt_len, axes=(16, 56, 56), theta=10000.0, scale_rope=True, device="cuda"):
+    """Rotation tables of the Qwen-Image block (QwenEmbedRope, ksana/models/qwen/attention.py:62-142), in the
+    row-per-coordinate-index form rmsnorm_rope_inplace reads: (img_table, txt_table), each (tab, n_f, n_h).
+
+    Image rows: row r holds the frame angle of frame r, the angle of the r-th (centred when scale_rope) image
+    row and of the r-th image column.  Text rows: row t holds the angles of position t0 + t on all three axes.
+    """
+    Fr, Hh, Ww = (int(v) for v in img_grid)
+    inv = [1.0 / torch.pow(theta, torch.arange(0, d, 2, dtype=torch.float64) / d) for d in axes]
+    n = max(Fr, Hh, Ww)
+
+    def centred(m):
+        return torch.cat([torch.arange(-(m - m // 2), 0), torch.arange(0, m // 2)]).to(torch.float64)
+
+    fpos = torch.arange(n, dtype=torch.float64)
+    hpos = torch.zeros(n, dtype=torch.float64)
+    wpos = torch.zeros(n, dtype=torch.float64)
+    hpos[:Hh] = centred(Hh) if scale_rope else torch.arange(Hh, dtype=torch.float64)
+    wpos[:Ww] = centred(Ww) if scale_rope else torch.arange(Ww, dtype=torch.float64)
+    ang = torch.cat([torch.outer(fpos, inv[0]), torch.outer(hpos, inv[1]), torch.outer(wpos, inv[2])], dim=1)
+    img = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous().to(device)
+    t0 = max(Hh // 2, Ww // 2) if scale_rope else max(Hh, Ww)
+    tpos = torch.arange(t0, t0 + txt_len, dtype=torch.float64)
+    tang = torch.cat([torch.outer(tpos, i) for i in inv], dim=1)
+    txt = torch.stack([torch.cos(tang), torch.sin(tang)], dim=-1).to(torch.float32).contiguous().to(device)
+    return (img, axes[0] // 2, axes[1] // 2), (txt, axes[0] // 2, axes[1] // 2)

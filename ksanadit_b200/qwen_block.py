@@ -1,0 +1,149 @@
+"""Qwen-Image dual-stream (MMDiT) block on the B200 kernels: the fused form of
+``QwenImageTransformerBlock.forward`` + ``QwenDoubleStreamAttention.forward``.
+
+Same parameters (state-dict names) and inputs as KsanaDiT's block
+(ksana/models/qwen/transformer.py:122-241, ksana/models/qwen/attention.py:221-371), run as
+
+  per stream: adaLN+quant -> fused QKV GEMM written straight into the joint [text; image] buffer ->
+              per-head RMSNorm + RoPE in place
+  joint:      K mean, INT8 Q/K, FP8 V quantisers -> one INT8/FP8 attention over text+image tokens
+  per stream: quant -> out-projection GEMM (+ gated residual) -> adaLN+quant -> MLP up GEMM (+GELU-tanh) ->
+              quant -> MLP down GEMM (+ gated residual)
+
+Single GPU only for now (the Ulysses variant replicates the text stream and slices its heads,
+qwen/attention.py:298-318; not built yet).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib, ops
+from .linear import B200Fp8Linear, quantize_weight_per_channel
+
+HEAD = 128
+
+
+class B200QwenBlock(torch.nn.Module):
+    def __init__(self, dim, num_heads, ffn_dim=None, eps=1e-6, device="cuda", dtype=torch.bfloat16):
+        super().__init__()
+        if dim != num_heads * HEAD:
+            raise _lib.KsanaB200Error(f"head size {dim // num_heads} is not supported (only {HEAD})")
+        self.dim, self.num_heads, self.eps, self.dtype = dim, num_heads, eps, dtype
+        self.ffn_dim = ffn_dim or 4 * dim  # FeedForward(mult=4), qwen/attention.py:191-192
+        kw = dict(device=device, dtype=dtype)
+        self.img_mod = torch.nn.Sequential(torch.nn.SiLU(), B200Fp8Linear(dim, 6 * dim, **kw))
+        self.txt_mod = torch.nn.Sequential(torch.nn.SiLU(), B200Fp8Linear(dim, 6 * dim, **kw))
+        self.attn = torch.nn.Module()
+        self.attn.to_qkv = B200Fp8Linear(dim, 3 * dim, **kw)
+        self.attn.add_qkv_proj = B200Fp8Linear(dim, 3 * dim, **kw)
+        self.attn.to_out = torch.nn.ModuleList([B200Fp8Linear(dim, dim, **kw), torch.nn.Identity()])
+        self.attn.to_add_out = B200Fp8Linear(dim, dim, **kw)
+        for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+            m = torch.nn.Module()
+            m.weight = torch.nn.Parameter(torch.ones(HEAD, device=device, dtype=torch.float32), requires_grad=False)
+            setattr(self.attn, n, m)
+        for s in ("img_mlp", "txt_mlp"):
+            mlp = torch.nn.Module()
+            act = torch.nn.Module()
+            act.proj = B200Fp8Linear(dim, self.ffn_dim, **kw)
+            mlp.net = torch.nn.ModuleList([act, torch.nn.Identity(), B200Fp8Linear(self.ffn_dim, dim, **kw)])
+            setattr(self, s, mlp)
+
+    # ------------------------------------------------------------------ parameters
+    def _linears(self):
+        return {
+            "img_mod.1": self.img_mod[1], "txt_mod.1": self.txt_mod[1], "attn.to_qkv": self.attn.to_qkv,
+            "attn.add_qkv_proj": self.attn.add_qkv_proj, "attn.to_out.0": self.attn.to_out[0], "attn.to_add_out": self.attn.to_add_out,
+            "img_mlp.net.0.proj": self.img_mlp.net[0].proj, "img_mlp.net.2": self.img_mlp.net[2],
+            "txt_mlp.net.0.proj": self.txt_mlp.net[0].proj, "txt_mlp.net.2": self.txt_mlp.net[2],
+        }
+
+    @staticmethod
+    def _set_linear(lin, w, b, scale=None):
+        dev = lin.weight.device
+        if w.dtype == torch.float8_e4m3fn:
+            wq, s = w, (torch.ones((), dtype=torch.float32) if scale is None else scale.float())
+        else:
+            wq, s = quantize_weight_per_channel(w.to(dev))
+        lin.weight = torch.nn.Parameter(wq.to(dev).contiguous(), requires_grad=False)
+        lin.scale_weight = torch.nn.Parameter(s.to(dev), requires_grad=False)
+        lin._w_scale_vec = None
+        if b is not None:
+            lin.bias = torch.nn.Parameter(b.to(dev, lin.compute_dtype), requires_grad=False)
+
+    def load_block_state_dict(self, sd: dict):
+        """State dict with QwenImageTransformerBlock's names; separate to_q/to_k/to_v (and add_*_proj) are fused,
+        high-precision weights are quantised per output channel."""
+        from .fuse_qkv import remap_qkv_weights
+        sd = dict(sd)
+        dev = self.attn.norm_q.weight.device
+        for names in (("attn.to_q", "attn.to_k", "attn.to_v"), ("attn.add_q_proj", "attn.add_k_proj", "attn.add_v_proj")):
+            if names[0] + ".weight" in sd and sd[names[0] + ".weight"].dtype != torch.float8_e4m3fn:
+                for n in names:
+                    wq, s = quantize_weight_per_channel(sd[n + ".weight"].to(dev))
+                    sd[n + ".weight"], sd[n + ".scale_weight"] = wq, s
+        remap_qkv_weights(sd, [("attn.to_q", "attn.to_k", "attn.to_v", "attn.to_qkv"),
+                               ("attn.add_q_proj", "attn.add_k_proj", "attn.add_v_proj", "attn.add_qkv_proj")])
+        for name, lin in self._linears().items():
+            self._set_linear(lin, sd[name + ".weight"], sd.get(name + ".bias"), sd.get(name + ".scale_weight"))
+        for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+            getattr(self.attn, n).weight = torch.nn.Parameter(sd[f"attn.{n}.weight"].float().to(dev).contiguous(), requires_grad=False)
+        return self
+
+    def random_init(self, seed: int, std: float = 0.02):
+        dev = self.attn.norm_q.weight.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        for lin in self._linears().values():
+            w = (torch.randn(lin.out_features, lin.in_features, device=dev, generator=g) * std).to(self.dtype)
+            b = (torch.randn(lin.out_features, device=dev, generator=g) * std).to(self.dtype)
+            self._set_linear(lin, w, b)
+        for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+            getattr(self.attn, n).weight = torch.nn.Parameter((1 + 0.1 * torch.randn(HEAD, device=dev, generator=g)).float(), requires_grad=False)
+        return self
+
+    # ------------------------------------------------------------------ forward
+    def _stream_tail(self, x, attn_out, gate1, mod2, out_lin, mlp):
+        """x + gate1 * out(attn_out), then x + gate2 * mlp(modulate(LN(x)))  (transformer.py:225-234)."""
+        aq, sa = ops.quant_fp8_rowwise(attn_out)
+        x = out_lin.forward_quantized(aq, sa, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=gate1)
+        shift2, scale2, gate2 = mod2
+        xq, sx = ops.adaln_quant_fp8(x, shift2, scale2, self.eps, round_product=True)
+        h = mlp.net[0].proj.forward_quantized(xq, sx, self.dtype, _lib.EPI_GELU_TANH)
+        hq, hs = ops.quant_fp8_rowwise(h)
+        return mlp.net[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=gate2, out=x)
+
+    def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, img_grid=None, **_):
+        """hidden_states [1, Li, C] (image), encoder_hidden_states [1, Lt, C] (text), temb [1, C];
+        img_grid (F, H, W) of the image tokens.  Returns (text, image) like the reference block.
+        ``image_rotary_emb`` is accepted for signature compatibility; the rotation tables are rebuilt from the
+        same formula (QwenEmbedRope) for ``img_grid`` and the text length."""
+        if hidden_states.shape[0] != 1:
+            raise _lib.KsanaB200Error("batch 1 only")
+        if img_grid is None:
+            raise ValueError("img_grid=(F, H, W) is required")
+        img, txt = hidden_states[0], encoder_hidden_states[0]
+        Li, C = img.shape
+        Lt = txt.shape[0]
+        H = self.num_heads
+        L = Lt + Li
+        img_tab, txt_tab = ops.qwen_rope_tables(img_grid, Lt, device=img.device)
+        st = torch.nn.functional.silu(temb)
+        imod = self.img_mod[1](st)[0].view(2, 3, 1, C)  # [mod1|mod2] x [shift|scale|gate]
+        tmod = self.txt_mod[1](st)[0].view(2, 3, 1, C)
+
+        qkv = torch.empty(L, 3 * C, dtype=self.dtype, device=img.device)  # joint buffer, text rows first (attention.py:355-357)
+        a = self.attn
+        for x, mod, lin, nq, nk, rows, tab, grid, diag in (
+            (txt, tmod, a.add_qkv_proj, a.norm_added_q, a.norm_added_k, slice(0, Lt), txt_tab, (Lt, 1, 1), True),
+            (img, imod, a.to_qkv, a.norm_q, a.norm_k, slice(Lt, L), img_tab, img_grid, False),
+        ):
+            xq, sx = ops.adaln_quant_fp8(x, mod[0, 0], mod[0, 1], self.eps, round_product=True)
+            lin.forward_quantized(xq, sx, self.dtype, out=qkv[rows])
+            ops.rmsnorm_rope_inplace(qkv[rows, :C], nq.weight, self.eps, tab, grid, per_head=True, diag=diag)
+            ops.rmsnorm_rope_inplace(qkv[rows, C:2 * C], nk.weight, self.eps, tab, grid, per_head=True, diag=diag)
+        t = qkv.view(L, 3, H, HEAD)
+        o = ops.sage_attention(t[:, 0], t[:, 1], t[:, 2]).view(L, C)
+        txt = self._stream_tail(txt, o[:Lt], tmod[0, 2], tmod[1], a.to_add_out, self.txt_mlp)
+        img = self._stream_tail(img, o[Lt:], imod[0, 2], imod[1], a.to_out[0], self.img_mlp)
+        return txt.unsqueeze(0), img.unsqueeze(0)

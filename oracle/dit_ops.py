@@ -290,8 +290,8 @@ def qwen_block_forward(p, img, txt, temb, img_ang, txt_ang, linear="fp8", attn="
     C = img.shape[-1]
     d = C // n
     st = F.silu(temb)[None]
-    img_mod = p["img_mod"].fp32(st)[0].chunk(2, dim=-1)  # modulation Linear stays high precision (tiny M)
-    txt_mod = p["txt_mod"].fp32(st)[0].chunk(2, dim=-1)
+    img_mod = lin(p["img_mod"], st)[0].chunk(2, dim=-1)  # every ops.Linear of the block is the FP8 Linear
+    txt_mod = lin(p["txt_mod"], st)[0].chunk(2, dim=-1)
 
     def mod(x, m):  # transformer.py:171-194
         shift, scale, gate = m.chunk(3, dim=-1)

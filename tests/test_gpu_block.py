@@ -107,3 +107,61 @@ def test_linear_module_forward_2d_3d():
     assert out.shape == (2, 33, 256) and out.dtype == torch.bfloat16
     assert max_abs_rel(out.cpu().float(), ref.float()) <= 1e-2
     assert lin(x[0].cuda()).shape == (33, 256)
+
+
+def _qwen_state_dict(p):
+    """Oracle Qwen block parameters -> a state dict with QwenImageTransformerBlock's parameter names."""
+    sd = {}
+    for a, b in (("img_mod.1", "img_mod"), ("txt_mod.1", "txt_mod"), ("attn.to_q", "to_q"), ("attn.to_k", "to_k"),
+                 ("attn.to_v", "to_v"), ("attn.add_q_proj", "add_q_proj"), ("attn.add_k_proj", "add_k_proj"),
+                 ("attn.add_v_proj", "add_v_proj"), ("attn.to_out.0", "to_out"), ("attn.to_add_out", "to_add_out"),
+                 ("img_mlp.net.0.proj", "img_mlp.0"), ("img_mlp.net.2", "img_mlp.2"),
+                 ("txt_mlp.net.0.proj", "txt_mlp.0"), ("txt_mlp.net.2", "txt_mlp.2")):
+        sd[a + ".weight"] = p[b].w
+        sd[a + ".bias"] = p[b].b
+    for nm in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+        sd[f"attn.{nm}.weight"] = p[nm]
+    return sd
+
+
+@pytest.mark.parametrize("dim,ffn,heads,grid,Lt", [(256, 1024, 2, (1, 6, 8), 10), (1024, 4096, 8, (1, 24, 20), 77)])
+def test_qwen_block_matches_oracle(dim, ffn, heads, grid, Lt):
+    from ksanadit_b200 import _lib
+    from ksanadit_b200.qwen_block import B200QwenBlock
+    p = D.make_qwen_block_params(dim, ffn, heads, seed=5)
+    for nm in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+        p[nm] = p[nm].to(torch.bfloat16)  # the reference keeps these weights in the run dtype
+    Li = grid[0] * grid[1] * grid[2]
+    g = torch.Generator().manual_seed(9)
+    img = D.make_activations(Li, dim, seed=6)
+    txt = torch.randn(Lt, dim, generator=g).to(torch.bfloat16)
+    temb = torch.randn(dim, generator=g).to(torch.bfloat16)
+    ia, ta = D.qwen_rope_angles(grid, Lt)
+    i_ref, t_ref = D.qwen_block_forward(p, img, txt, temb, ia, ta, linear="fp8", attn="sage")
+    blk = B200QwenBlock(dim, heads, ffn, device="cuda").load_block_state_dict(_qwen_state_dict(p))
+    with torch.no_grad():
+        t_out, i_out = blk(img[None].cuda(), txt[None].cuda(), temb[None].cuda(), img_grid=grid)
+    _lib.assert_device_ok()
+    for out, ref in ((i_out[0].cpu().float(), i_ref.float()), (t_out[0].cpu().float(), t_ref.float())):
+        assert cosine(out, ref) >= BLOCK_COS and max_abs_rel(out, ref) <= BLOCK_MAR
+    i_exact, t_exact = D.qwen_block_forward(p, img, txt, temb, ia, ta, linear="fp32", attn="sdpa")
+    assert cosine(i_out[0].cpu().float(), i_exact.float()) >= BLOCK_COS
+
+
+def test_per_head_rmsnorm_and_qwen_rope():
+    from ksanadit_b200 import ops
+    heads, grid, Lt = 3, (1, 6, 10), 7
+    Li = grid[1] * grid[2]
+    g = torch.Generator().manual_seed(4)
+    w = (1 + 0.1 * torch.randn(128, generator=g))
+    ia, ta = D.qwen_rope_angles(grid, Lt)
+    img_tab, txt_tab = ops.qwen_rope_tables(grid, Lt)
+    for L, ang, tab, gr, diag in ((Li, ia, img_tab, grid, False), (Lt, ta, txt_tab, (Lt, 1, 1), True)):
+        x = (torch.randn(L, heads * 128, generator=g) * 2).to(torch.bfloat16)
+        n = D.rmsnorm_heads(x.view(L, heads, 128), w.to(torch.bfloat16))
+        ref = D.apply_rope_angles(n, ang).reshape(L, heads * 128)
+        xd = x.cuda()
+        ops.rmsnorm_rope_inplace(xd, w.to(torch.bfloat16).float().cuda(), 1e-6, tab, gr, per_head=True, diag=diag)
+        d = (xd.cpu().float() - ref.float()).abs()
+        assert float(d.max()) <= 2 ** -6 * float(ref.float().abs().max())
+        assert cosine(xd.cpu(), ref) > 0.99999
