@@ -169,11 +169,12 @@ int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H,
  * Block-sparse: tile_offsets int32 [Lq_pad/128 + 1] and tile_entries int32 [nnz] (shared by all heads);
  * entry = kv_tile*4 + keep bits (bit0: tokens 0-63 of the 128-token tile, bit1: tokens 64-127), ascending
  * kv_tile within a row.  NULL/NULL = dense.  A Q block with an empty list produces zeros.
- * counter: one int32 of zero-initialised scratch used as the persistent work queue head (NULL = static
- * round-robin schedule). */
+ * q_order (optional, int32 [Lq_pad/128]): a permutation of the Q blocks; the CTAs walk the blocks of a head in
+ * this order (pass the blocks sorted by decreasing list length to balance a ragged block-sparse mask over the
+ * persistent CTAs).  NULL = ascending. */
 int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vs,
                   int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets, const int32_t* tile_entries,
-                  void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride, int32_t* counter,
+                  const int32_t* q_order, void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride,
                   ksb_stream_t stream);
 
 #ifdef __cplusplus

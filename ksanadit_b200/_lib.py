@@ -42,7 +42,7 @@ SIGNATURES = {
     "ksb_sage_quant_v_fp8_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                              c_void_p]),
     "ksb_sage_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                              c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]),
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]),
 }
 
 _lib = None

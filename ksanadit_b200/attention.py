@@ -78,9 +78,9 @@ def _run_sage(query, key, value, tile_lists=None):
         query, key, value = (t.to(torch.bfloat16) for t in (query, key, value))
     B, Lq, H, D = query.shape
     out = torch.empty(B, Lq, H, D, dtype=query.dtype, device=query.device)
-    offs, ents = tile_lists if tile_lists is not None else (None, None)
+    offs, ents, order = tile_lists if tile_lists is not None else (None, None, None)
     for b in range(B):
-        ops.sage_attention(query[b], key[b], value[b], tile_offsets=offs, tile_entries=ents, out=out[b])
+        ops.sage_attention(query[b], key[b], value[b], tile_offsets=offs, tile_entries=ents, out=out[b], tile_order=order)
     return out if out.dtype == orig else out.to(orig)
 
 
@@ -169,7 +169,8 @@ class B200RadialSageAttentionImpl(KsanaAttentionBackendImpl):
                 ents = np.zeros(1, dtype=np.int32)  # keep a valid pointer for an all-empty mask
             if len(cache) >= self._max_cache_size:
                 cache.popitem(last=False)
-            cache[key] = (torch.from_numpy(offs).to(device), torch.from_numpy(ents).to(device))
+            order = radial_mask.longest_first_order(offs)
+            cache[key] = (torch.from_numpy(offs).to(device), torch.from_numpy(ents).to(device), torch.from_numpy(order).to(device))
         return cache[key]
 
 

@@ -48,6 +48,7 @@ struct Params {
   int H, Lq, Lk, nq, nkv;
   const int32_t* offsets;
   const int32_t* entries;
+  const int32_t* order;  // optional permutation of the Q blocks of a head (longest list first)
   void* out;
   int64_t out_ts, out_hs;
   int* status;
@@ -62,6 +63,7 @@ __device__ __forceinline__ Work get_work(const Params& p, int idx) {
   Work w;
   w.h = idx / p.nq;
   w.qt = idx - w.h * p.nq;
+  if (p.order) w.qt = p.order[w.qt];
   if (p.offsets) {
     const int a = p.offsets[w.qt], b = p.offsets[w.qt + 1];
     w.n = b - a;
@@ -464,9 +466,8 @@ extern "C" int ksb_debug_attn_phase_cycles(unsigned long long* out16, int reset)
 
 extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
                              const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,
-                             const int32_t* tile_entries, void* out, int dtype, int64_t out_token_stride,
-                             int64_t out_head_stride, int32_t* counter, ksb_stream_t stream) {
-  (void)counter;
+                             const int32_t* tile_entries, const int32_t* q_order, void* out, int dtype,
+                             int64_t out_token_stride, int64_t out_head_stride, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (H <= 0 || Lq <= 0 || Lk <= 0) return fail(KSB_ERR_INVALID, "bad shape H=%lld Lq=%lld Lk=%lld", (long long)H, (long long)Lq, (long long)Lk);
   if (!q8 || !qs || !k8 || !ks || !vt || !vs || !out) return fail(KSB_ERR_INVALID, "null pointer");
@@ -481,7 +482,7 @@ extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, co
   attn::Params p{};
   p.qs = qs; p.ks = ks; p.vs = vs;
   p.H = (int)H; p.Lq = (int)Lq; p.Lk = (int)Lk; p.nq = (int)nq; p.nkv = (int)nkv;
-  p.offsets = tile_offsets; p.entries = tile_entries;
+  p.offsets = tile_offsets; p.entries = tile_entries; p.order = q_order;
   p.out = out; p.out_ts = out_token_stride; p.out_hs = out_head_stride;
   p.status = status_words();
   if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");

@@ -65,16 +65,18 @@ def run_attn(a):
     k8, ks = ops.sage_quant_int8(k, 64, mean=km)
     vt, vs = ops.sage_quant_v(v)
     out = torch.empty(L, H, 128, dtype=torch.bfloat16, device="cuda")
-    offs = ents = None
+    offs = ents = order = None
     pairs = ((L + 127) // 128) ** 2
     if a.density < 1.0:
         tpf = max(128, L // 21)
         m = radial_mask.bernoulli_frame_tile_mask(L, tpf, seed=0)
         o, e = radial_mask.compact_tile_lists(radial_mask.expand_to_kernel_granularity(m, 128))
         offs, ents = torch.from_numpy(o).cuda(), torch.from_numpy(e).cuda()
+        if a.sorted:
+            order = torch.from_numpy(radial_mask.longest_first_order(o)).cuda()
         pairs = int(e.size)
         print(f"  tile mask density {m.mean():.3f}")
-    t = timeit(lambda: ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, tile_offsets=offs, tile_entries=ents, out=out), a.iters, a.warmup)
+    t = timeit(lambda: ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, tile_offsets=offs, tile_entries=ents, out=out, tile_order=order), a.iters, a.warmup)
     fl = 4.0 * H * 128 * 128 * 128 * pairs
     print(f"sage_attn L={L} H={H} tiles/head={pairs}: {t:.3f} ms  {fl / t / 1e9:.1f} TFLOP/s (visited tiles)")
     if a.compare and L <= 16384:
@@ -143,6 +145,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kind", choices=["gemm", "attn", "quant", "prepass", "qwen"])
     ap.add_argument("--layers", type=int, default=60)
+    ap.add_argument("--sorted", action="store_true", help="block-sparse: walk the Q blocks longest list first")
     ap.add_argument("--M", type=int, default=75600)
     ap.add_argument("--N", type=int, default=5120)
     ap.add_argument("--K", type=int, default=5120)

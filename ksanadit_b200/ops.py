@@ -225,9 +225,10 @@ def q_premul(head_dim: int, sm_scale: float | None = None) -> float:
     return float(torch.tensor(sc * LOG2E, dtype=torch.float64).to(torch.float32))
 
 
-def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, tile_offsets=None, tile_entries=None, out=None):
+def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, tile_offsets=None, tile_entries=None, out=None,
+                   tile_order=None):
     """Quantised operands -> out [Lq, H, 128]."""
-    _cuda(q8, qs, k8, ks, vt, vs, tile_offsets, tile_entries, out)
+    _cuda(q8, qs, k8, ks, vt, vs, tile_offsets, tile_entries, tile_order, out)
     H = q8.shape[0]
     if out is None:
         out = torch.empty(Lq, H, 128, dtype=out_dtype, device=q8.device)
@@ -235,19 +236,19 @@ def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, til
     dt = _lib.BF16 if out.dtype == torch.bfloat16 else _lib.FP16
     STATS.timed(("attn", H, Lq, Lk, tile_offsets is not None), lambda: _lib.check(
         _lib.load().ksb_sage_attn(_p(q8), _p(qs), _p(k8), _p(ks), _p(vt), _p(vs), H, Lq, Lk, _p(tile_offsets),
-                                  _p(tile_entries), _p(out), dt, out.stride(0), out.stride(1), None, _stream()),
+                                  _p(tile_entries), _p(tile_order), _p(out), dt, out.stride(0), out.stride(1), _stream()),
         "ksb_sage_attn"))
     STATS.count(1)
     return out
 
 
-def sage_attention(q, k, v, sm_scale=None, tile_offsets=None, tile_entries=None, out=None):
+def sage_attention(q, k, v, sm_scale=None, tile_offsets=None, tile_entries=None, out=None, tile_order=None):
     """q [Lq,H,128], k,v [Lk,H,128] half -> [Lq,H,128]: K smoothing, INT8 Q/K, FP8 V, attention core."""
     km = sage_kmean(k)
     q8, qs = sage_quant_int8(q, Q_BLOCK, premul=q_premul(q.shape[-1], sm_scale))
     k8, ks = sage_quant_int8(k, K_BLOCK, mean=km)
     vt, vs = sage_quant_v(v)
-    return sage_attn_core(q8, qs, k8, ks, vt, vs, q.shape[0], k.shape[0], q.dtype, tile_offsets, tile_entries, out)
+    return sage_attn_core(q8, qs, k8, ks, vt, vs, q.shape[0], k.shape[0], q.dtype, tile_offsets, tile_entries, out, tile_order)
 
 
 # ----------------------------------------------------------------------------- RMSNorm + RoPE (in place)

@@ -101,3 +101,9 @@ def compact_tile_lists(mask_q128_k64: np.ndarray):
     np.cumsum(counts, out=offsets[1:])
     entries = (cols.astype(np.int32) * 4 + halves[rows, cols]).astype(np.int32)
     return offsets, entries
+
+
+def longest_first_order(offsets: np.ndarray) -> np.ndarray:
+    """Permutation of the Q blocks by decreasing list length (stable), for the kernel's ``q_order`` argument."""
+    counts = np.diff(np.asarray(offsets, dtype=np.int64))
+    return np.argsort(-counts, kind="stable").astype(np.int32)

@@ -50,7 +50,7 @@ class B200WanBlock(torch.nn.Module):
         self.cross_attn_norm = cross_attn_norm
         self.ffn = torch.nn.ModuleList([B200Fp8Linear(dim, ffn_dim, **kw), torch.nn.Identity(), B200Fp8Linear(ffn_dim, dim, **kw)])
         self.modulation = torch.nn.Parameter(torch.zeros(1, 6, dim, device=device, dtype=dtype), requires_grad=False)
-        self.tile_lists = tile_lists  # (offsets, entries) for block-sparse self-attention, or None
+        self.tile_lists = tile_lists  # (offsets, entries, order) for block-sparse self-attention, or None
         self.cache_context = cache_context  # keep the quantised context K/V across steps (off: recomputed every call)
         self._ones = None
         self._ctx_cache = None
@@ -157,8 +157,8 @@ class B200WanBlock(torch.nn.Module):
         q8, qs = ops.sage_quant_int8(q3, ops.Q_BLOCK, premul=ops.q_premul(HEAD))
         k8, ks = ops.sage_quant_int8(k3, ops.K_BLOCK, mean=km)
         vt, vs = ops.sage_quant_v(v3)
-        offs, ents = self.tile_lists if self.tile_lists is not None else (None, None)
-        o = ops.sage_attn_core(q8, qs, k8, ks, vt, vs, Lf, Lf, self.dtype, offs, ents)  # [L*P, H/P, D]
+        offs, ents, order = self.tile_lists if self.tile_lists is not None else (None, None, None)
+        o = ops.sage_attn_core(q8, qs, k8, ks, vt, vs, Lf, Lf, self.dtype, offs, ents, tile_order=order)  # [L*P, H/P, D]
         if P > 1:
             o = distribute.sequence_to_heads(o)  # [L, H, D]
         return o.reshape(L, C)

@@ -23,18 +23,21 @@ def _qkv(Lq, Lk, H, seed, dtype=torch.bfloat16):
     return q, k, v
 
 
-def _core_from_oracle_operands(q, k, v, tile_mask=None):
+def _core_from_oracle_operands(q, k, v, tile_mask=None, sorted_order=False):
     """Runs the GPU core on the oracle's quantised tensors, so only the core differs."""
     from ksanadit_b200 import _lib, ops
     pp = Sg.sage_prepass(q, k, v)
-    offs = ents = None
+    offs = ents = order = None
     if tile_mask is not None:
+        from ksanadit_b200 import radial_mask as PM
         o, e = R.tile_lists(tile_mask)
         offs, ents = torch.from_numpy(o).cuda(), torch.from_numpy(e).cuda()
         if ents.numel() == 0:
             ents = torch.zeros(1, dtype=torch.int32, device="cuda")
+        if sorted_order:
+            order = torch.from_numpy(PM.longest_first_order(o)).cuda()
     out = ops.sage_attn_core(pp["q8"].cuda(), pp["qs"].cuda(), pp["k8"].cuda(), pp["ks"].cuda(), pp["vt8"].cuda(),
-                             pp["vs"].cuda(), q.shape[0], k.shape[0], q.dtype, offs, ents)
+                             pp["vs"].cuda(), q.shape[0], k.shape[0], q.dtype, offs, ents, tile_order=order)
     _lib.assert_device_ok()
     ref = Sg.sage_core(pp, q.shape[0], k.shape[0], None if tile_mask is None else torch.from_numpy(tile_mask), out_dtype=torch.float32)
     return out.cpu().float(), ref
@@ -61,14 +64,15 @@ def test_large_score_range_exercises_rescale():
     assert cosine(out, ref) >= ATT_COS and max_abs_rel(out, ref) <= ATT_MAR
 
 
-def test_sparse_core_matches_oracle():
+@pytest.mark.parametrize("sorted_order", [False, True])
+def test_sparse_core_matches_oracle(sorted_order):
     Lq = Lk = 128 * 9 + 50
     q, k, v = _qkv(Lq, Lk, 2, seed=7)
     m = R.expand_to_q128_k64(R.bernoulli_frame_mask(Lq, 300, seed=2), 128)
     m[3, :] = False          # a Q block with nothing to attend to -> zeros
     m[5, 2] = False          # a tile with only its second half kept
     m[5, 3] = True
-    out, ref = _core_from_oracle_operands(q, k, v, m)
+    out, ref = _core_from_oracle_operands(q, k, v, m, sorted_order)
     assert float(out[3 * 128:4 * 128].abs().max()) == 0.0
     assert cosine(out, ref) >= ATT_COS and max_abs_rel(out, ref) <= ATT_MAR
 
