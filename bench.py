@@ -31,6 +31,9 @@ sys.path.insert(0, ROOT)
 
 # Wan2.2-T2V-14B block stack (ksana/settings/wan/modules/14b.yaml:16-26) at 720p x 81 frames
 W14 = dict(layers=40, dim=5120, ffn=13824, heads=40, grid=(21, 45, 80), text_len=512)
+# DRAM bytes (read + write) of one self-attention launch per head at 75 600 tokens, from the one-pass ncu capture of
+# the full-size launch summarised in profiles/sage_attn_kernel_L16384_H16_and_full.md (3.26 GB for 40 heads)
+ATTN_DRAM_BYTES_PER_HEAD = 3.262e9 / 40
 METRIC = "wan14b_dit_step_tflops"
 UNIT = "TFLOP/s"
 
@@ -274,7 +277,9 @@ def run_ours(args):
                     "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": launches,
             "roofline": {"kernel": "sage_attn_kernel (self-attention)", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
-                         "unit": "TFLOP/s", "frac": (achieved / fp8_peak) if achieved else None, "traffic": None,
+                         "unit": "TFLOP/s", "frac": (achieved / fp8_peak) if achieved else None,
+                         "traffic": ATTN_DRAM_BYTES_PER_HEAD * Hl if L == 75600 else None,
+                         "algorithmic_flop_per_launch": att_flop,
                          "peak_source": "of measured: torch._scaled_mm e4m3 8192^3 best of 10 in this run (MEASURED_PEAKS.json holds "
                                         f"bf16 only: {peaks.get('bf16_tflops')} TF/s burst)",
                          "launches": n_att, "ms_per_launch": (ms_att / n_att) if n_att else None,

@@ -10,8 +10,10 @@
 //               so the epilogue of tile i overlaps the main loop of tile i+1
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (one row per thread), apply scales / bias / fused
 //               GELU-tanh or gated residual, convert to half, store
-// Tiles are visited in groups of GROUP_M row-tiles so that CTAs running at the same time share operand
-// tiles in L2.  Ragged M, N, K edges rely on TMA zero fill for loads and on predicated stores.
+// Tiles are visited in groups of `group_m` row-tiles (all column tiles of a group, row-tile fastest) so that
+// CTAs running at the same time share operand tiles in L2.  The weight is streamed from HBM once per group,
+// the group's activation rows stay in L2 while the group sweeps the columns: the host picks the group height so
+// that those rows take about 32 MB (32 row-tiles at K = 5120, 16 at K = 13824).  Ragged M, N, K edges rely on TMA zero fill for loads and on predicated stores.
 //
 // Tensor-bound: 2*M*N*K flop per launch; minimal traffic M*K + N*K + 2*M*N bytes.
 #include "../../include/ksana_b200.h"
@@ -26,7 +28,6 @@ constexpr int UMMA_K = 32;
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
-constexpr int GROUP_M = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID = 1;
 // dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers]
@@ -34,6 +35,7 @@ constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256;
 
 struct Params {
   int M, N, K;
+  int group_m;  // row-tiles per rasterisation group
   const float* sa;
   const float* sw;
   const void* bias;
@@ -47,11 +49,11 @@ struct Params {
   int* status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int per_group = GROUP_M * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
   const int g = tile / per_group;
-  const int first_m = g * GROUP_M;
-  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int first_m = g * group_m;
+  const int rows = min(group_m, tiles_m - first_m);
   const int r = tile - g * per_group;
   tm = first_m + r % rows;
   tn = r / rows;
@@ -109,7 +111,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
         for (int k = 0; k < num_k; ++k, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, p.status, (KERNEL_ID << 16) | 1)) { ok = false; break; }
@@ -154,7 +156,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     T* out = static_cast<T*>(p.out);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       // All four epilogue warps leave together if any of their waits ran out (a warp must never be
       // left alone at the named barrier below); the same barrier protects the reuse of colp.
@@ -264,6 +266,8 @@ extern "C" int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, 
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = out; p.ldo = ldo; p.epilogue = epilogue;
   p.resid = resid; p.ldr = ldr; p.gate = gate; p.gate_rows = gate_rows;
+  p.group_m = 64;
+  while (p.group_m > 8 && (int64_t)p.group_m * gemm::BM * K > (32ll << 20)) p.group_m >>= 1;
   p.status = status_words();
   if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");
   const int tiles = (int)((M + gemm::BM - 1) / gemm::BM) * (int)((N + gemm::BN - 1) / gemm::BN);
