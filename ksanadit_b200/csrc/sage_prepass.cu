@@ -70,19 +70,20 @@ __global__ void mean_finish_kernel(const float* __restrict__ partial, int chunks
 // grid (Lpad / BLOCK, H).  A block of BLOCK tokens x 128 channels lives in registers between the
 // absmax reduction and the quantisation.
 template <typename T, int BLOCK>
-__global__ void __launch_bounds__(THREADS) int8_block_quant_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs,
+__global__ void __launch_bounds__(BLOCK * 4) int8_block_quant_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs,
                                                                     float premul, const float* __restrict__ mean,
                                                                     int8_t* __restrict__ out, float* __restrict__ scale,
                                                                     int64_t Lpad) {
-  constexpr int VEC = BLOCK * D / 8 / THREADS;  // 16-byte vectors per thread (8 for 128 tokens, 4 for 64)
-  __shared__ float red[THREADS / 32];
+  constexpr int NT = BLOCK * 4;             // four threads per token: 512 threads for Q blocks, 256 for K blocks
+  constexpr int VEC = BLOCK * D / 8 / NT;   // 4 sixteen-byte vectors per thread
+  __shared__ float red[NT / 32];
   const int h = blockIdx.y, b = blockIdx.x;
   const int64_t l0 = (int64_t)b * BLOCK;
   float v[VEC][8];
   float am = 0.f;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    const int j = threadIdx.x + i * THREADS;
+    const int j = threadIdx.x + i * NT;
     const int r = j >> 4, c = (j & 15) * 8;
     const int64_t l = l0 + r;
     if (l < L) {
@@ -105,13 +106,13 @@ __global__ void __launch_bounds__(THREADS) int8_block_quant_kernel(const T* __re
   __syncthreads();
   am = red[0];
 #pragma unroll
-  for (int i = 1; i < THREADS / 32; ++i) am = fmaxf(am, red[i]);
+  for (int i = 1; i < NT / 32; ++i) am = fmaxf(am, red[i]);
   const float sc = (am > 0.f) ? __fdiv_rn(am, 127.f) : 1.f;
   const float inv = (am > 0.f) ? __fdiv_rn(127.f, am) : 1.f;
   if (threadIdx.x == 0) scale[(int64_t)h * (Lpad / BLOCK) + b] = sc;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    const int j = threadIdx.x + i * THREADS;
+    const int j = threadIdx.x + i * NT;
     const int r = j >> 4, c = (j & 15) * 8;
     uint32_t w[2] = {0, 0};
 #pragma unroll
@@ -177,15 +178,14 @@ __global__ void __launch_bounds__(THREADS) v_quant_transpose_kernel(const T* __r
 }
 
 // ---------------------------------------------------------------------------------- RMSNorm (+ RoPE) in place
-// Full-width RMSNorm over C = H*128 channels with an fp32 weight, optionally followed by the 3-axis
-// rotary embedding, applied in place to a [L, C] half view (row stride ld).  One CTA walks ROWS_PER_CTA
-// consecutive tokens; each thread owns fixed 8-channel vectors of the row, so it can also accumulate
-// the column sums of the values it writes (the K smoothing mean) without a second pass.
+// RMSNorm over all C = H*128 channels (or over each head's 128) with an fp32 weight, optionally followed by
+// the 3-axis rotary embedding, applied in place to a [L, C] half view (row stride ld).  A row is owned by
+// the 4 warps of a CTA (one 128-bit vector of 8 channels per thread and step), read once, held in registers
+// in packed form across the sum-of-squares reduction, and written once; many CTAs share an SM.
 // Rounding points follow the eager sequence: norm output rounded to half, rotation computed in fp32
 // (the eager path uses fp64) and rounded to half.
-constexpr int NR_THREADS = 256;
-constexpr int NR_MAX_VEC = 4;  // C <= 256 * 8 * 4 = 8192
-constexpr int NR_ROWS = 32;
+constexpr int NR_THREADS = 128;
+constexpr int NR_MAX_VEC = 8;  // C <= 128 * 8 * 8 = 8192
 
 struct RopeGrid {
   const float2* table;  // [table_len][64] (cos, sin); pair p of a head uses axis f for p < nf, then h, then w
@@ -195,51 +195,25 @@ struct RopeGrid {
   int diag;      // 1: one running position drives all three axes (text tokens of the Qwen-Image block)
 };
 
-template <typename T, bool ROPE, bool PER_HEAD>
-__global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
-                                                                  const float* __restrict__ w, float eps, RopeGrid rg,
-                                                                  float* __restrict__ colsum_partial) {
+template <typename T, bool ROPE, bool PER_HEAD, int NV>
+__global__ void __launch_bounds__(NR_THREADS, 4) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
+                                                                     const float* __restrict__ w, float eps, RopeGrid rg) {
   __shared__ float red[2][NR_THREADS / 32];
   const int nvec = C / 8;
-  const int64_t l0 = (int64_t)blockIdx.x * NR_ROWS;
-  const int64_t l1 = min(L, l0 + NR_ROWS);
-  float cs[NR_MAX_VEC][8];
-#pragma unroll
-  for (int i = 0; i < NR_MAX_VEC; ++i)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) cs[i][e] = 0.f;
-  // the next row is fetched while the current one is reduced and written
-  uint4 cur[NR_MAX_VEC], nxt[NR_MAX_VEC];
-#pragma unroll
-  for (int i = 0; i < NR_MAX_VEC; ++i) {
-    const int j = threadIdx.x + i * NR_THREADS;
-    cur[i] = (j < nvec) ? *reinterpret_cast<const uint4*>(x + l0 * ld + j * 8) : make_uint4(0, 0, 0, 0);
-  }
   int par = 0;
-  for (int64_t l = l0; l < l1; ++l, par ^= 1) {
+  for (int64_t l = blockIdx.x; l < L; l += gridDim.x, par ^= 1) {
     T* row = x + l * ld;
-    if (l + 1 < l1) {
+    uint4 cur[NV];
 #pragma unroll
-      for (int i = 0; i < NR_MAX_VEC; ++i) {
-        const int j = threadIdx.x + i * NR_THREADS;
-        nxt[i] = (j < nvec) ? *reinterpret_cast<const uint4*>(row + ld + j * 8) : make_uint4(0, 0, 0, 0);
-      }
+    for (int i = 0; i < NV; ++i) {
+      const int j = threadIdx.x + i * NR_THREADS;
+      cur[i] = (j < nvec) ? *reinterpret_cast<const uint4*>(row + j * 8) : make_uint4(0, 0, 0, 0);
     }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < NR_MAX_VEC; ++i) {
-      const T* t = reinterpret_cast<const T*>(&cur[i]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float f = HalfOps<T>::to_f(t[e]);
-        ss += f * f;
-      }
-    }
-    float rstd_v[NR_MAX_VEC];
+    float rstd_v[NV];
     if (PER_HEAD) {
-      // RMSNorm over each head's 128 channels: 16 consecutive 8-channel vectors, i.e. 16 consecutive lanes
+      // each head's 128 channels = 16 consecutive 8-channel vectors = 16 consecutive lanes
 #pragma unroll
-      for (int i = 0; i < NR_MAX_VEC; ++i) {
+      for (int i = 0; i < NV; ++i) {
         const T* t = reinterpret_cast<const T*>(&cur[i]);
         float hs = 0.f;
 #pragma unroll
@@ -252,15 +226,22 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
         rstd_v[i] = rsqrtf(hs / (float)D + eps);
       }
     } else {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const T* t = reinterpret_cast<const T*>(&cur[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float f = HalfOps<T>::to_f(t[e]);
+          ss += f * f;
+        }
+      }
       ss = warp_sum(ss);
       if ((threadIdx.x & 31) == 0) red[par][threadIdx.x >> 5] = ss;
       __syncthreads();
-      float tot = 0.f;
+      const float r = rsqrtf((red[par][0] + red[par][1] + red[par][2] + red[par][3]) / (float)C + eps);
 #pragma unroll
-      for (int i = 0; i < NR_THREADS / 32; ++i) tot += red[par][i];
-      const float r = rsqrtf(tot / (float)C + eps);
-#pragma unroll
-      for (int i = 0; i < NR_MAX_VEC; ++i) rstd_v[i] = r;
+      for (int i = 0; i < NV; ++i) rstd_v[i] = r;
     }
     int cf = 0, ch = 0, cw = 0;
     bool rotate = false;
@@ -277,7 +258,7 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
       }
     }
 #pragma unroll
-    for (int i = 0; i < NR_MAX_VEC; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int j = threadIdx.x + i * NR_THREADS;
       if (j < nvec) {
         const T* t = reinterpret_cast<const T*>(&cur[i]);
@@ -295,31 +276,15 @@ __global__ void __launch_bounds__(NR_THREADS) rmsnorm_rope_kernel(T* __restrict_
             const int coord = pr < rg.nf ? cf : (pr < rg.nf + rg.nh ? ch : cw);
             const float2 cssn = rg.table[(int64_t)coord * 64 + pr];
             const float a = y[e], b = y[e + 1];
-            y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(a * cssn.x - b * cssn.y));
-            y[e + 1] = HalfOps<T>::to_f(HalfOps<T>::from_f(a * cssn.y + b * cssn.x));
+            y[e] = a * cssn.x - b * cssn.y;
+            y[e + 1] = a * cssn.y + b * cssn.x;
           }
         }
         uint4 o;
         T* ot = reinterpret_cast<T*>(&o);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          ot[e] = HalfOps<T>::from_f(y[e]);
-          cs[i][e] += y[e];
-        }
+        for (int e = 0; e < 8; ++e) ot[e] = HalfOps<T>::from_f(y[e]);
         *reinterpret_cast<uint4*>(row + j * 8) = o;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < NR_MAX_VEC; ++i) cur[i] = nxt[i];
-  }
-  if (colsum_partial) {
-#pragma unroll
-    for (int i = 0; i < NR_MAX_VEC; ++i) {
-      const int j = threadIdx.x + i * NR_THREADS;
-      if (j < nvec) {
-        float* dst = colsum_partial + (int64_t)blockIdx.x * C + j * 8;
-        *reinterpret_cast<float4*>(dst) = make_float4(cs[i][0], cs[i][1], cs[i][2], cs[i][3]);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(cs[i][4], cs[i][5], cs[i][6], cs[i][7]);
       }
     }
   }
@@ -393,17 +358,16 @@ int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, in
 
 
 int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C) {
-  return ((L + prep::NR_ROWS - 1) / prep::NR_ROWS) * C;
+  return ((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK) * C;
 }
 
 int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, int per_head, float eps,
                              const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
                              int diag, float* colsum_partial, float* colmean, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
-  if (L <= 0 || C <= 0 || C % 128 != 0 || C > 256 * 8 * prep::NR_MAX_VEC) return fail(KSB_ERR_INVALID, "C=%lld must be a multiple of 128 and <= 8192", (long long)C);
+  if (L <= 0 || C <= 0 || C % 128 != 0 || C > prep::NR_THREADS * 8 * prep::NR_MAX_VEC) return fail(KSB_ERR_INVALID, "C=%lld must be a multiple of 128 and <= 8192", (long long)C);
   if (!x || !w || !aligned16(x) || !aligned16(w) || ld < C || ld % 8 != 0) return fail(KSB_ERR_INVALID, "x/w null, unaligned or bad row stride");
   if ((colsum_partial == nullptr) != (colmean == nullptr)) return fail(KSB_ERR_INVALID, "colsum_partial and colmean go together");
-  if (colsum_partial && !aligned16(colsum_partial)) return fail(KSB_ERR_INVALID, "colsum_partial must be 16-byte aligned");
   prep::RopeGrid rg{};
   if (rope_table) {
     if (nf < 0 || nh < 0 || nf + nh > 64 || F <= 0 || Hh <= 0 || Ww <= 0) return fail(KSB_ERR_INVALID, "bad rope grid");
@@ -413,19 +377,32 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
     rg.F = F; rg.Hh = Hh; rg.Ww = Ww; rg.pos0 = pos0; rg.diag = diag ? 1 : 0;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int blocks = (int)((L + prep::NR_ROWS - 1) / prep::NR_ROWS);
-#define KSB_LAUNCH_NR(T, R, P) prep::rmsnorm_rope_kernel<T, R, P><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg, colsum_partial)
+  const int64_t cap = (int64_t)sm_count() * 16;
+  const int blocks = (int)(L < cap ? L : cap);
+  const bool wide = C > prep::NR_THREADS * 8 * 4;  // more than 4 vectors per thread
+#define KSB_LAUNCH_NR(T, R, P, NV) prep::rmsnorm_rope_kernel<T, R, P, NV><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg)
+#define KSB_LAUNCH_NR3(T, R, P) do { if (wide) KSB_LAUNCH_NR(T, R, P, 8); else KSB_LAUNCH_NR(T, R, P, 4); } while (0)
 #define KSB_LAUNCH_NR2(T)                                                          \
   do {                                                                             \
-    if (rope_table) { if (per_head) KSB_LAUNCH_NR(T, true, true); else KSB_LAUNCH_NR(T, true, false); } \
-    else { if (per_head) KSB_LAUNCH_NR(T, false, true); else KSB_LAUNCH_NR(T, false, false); }           \
+    if (rope_table) { if (per_head) KSB_LAUNCH_NR3(T, true, true); else KSB_LAUNCH_NR3(T, true, false); } \
+    else { if (per_head) KSB_LAUNCH_NR3(T, false, true); else KSB_LAUNCH_NR3(T, false, false); }           \
   } while (0)
   if (dtype == KSB_BF16) KSB_LAUNCH_NR2(__nv_bfloat16); else KSB_LAUNCH_NR2(__half);
 #undef KSB_LAUNCH_NR2
+#undef KSB_LAUNCH_NR3
 #undef KSB_LAUNCH_NR
   if (int rc = check_launch("rmsnorm/rope")) return rc;
-  if (colsum_partial) {
-    prep::mean_finish_kernel<<<(int)((C + 255) / 256), 256, 0, st>>>(colsum_partial, blocks, (int)C, 1.0f / (float)L, colmean);
+  if (colmean) {
+    // per-channel mean of the values just written (the K smoothing vector): the column-reduction pass over x
+    // seen as [L, C/128, 128]
+    const int chunks = (int)((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK);
+    dim3 grid(chunks, (unsigned)(C / 128));
+    if (dtype == KSB_BF16)
+      prep::column_reduce_kernel<__nv_bfloat16, false><<<grid, prep::THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(x), L, ld, 128, colsum_partial, (int)(C / 128));
+    else
+      prep::column_reduce_kernel<__half, false><<<grid, prep::THREADS, 0, st>>>(static_cast<const __half*>(x), L, ld, 128, colsum_partial, (int)(C / 128));
+    if (int rc = check_launch("column sums")) return rc;
+    prep::mean_finish_kernel<<<(int)((C + 255) / 256), 256, 0, st>>>(colsum_partial, chunks, (int)C, 1.0f / (float)L, colmean);
     return check_launch("column mean");
   }
   return 0;
@@ -440,7 +417,7 @@ int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t 
   const int64_t Lpad = prep::pad128(L);
   dim3 grid((unsigned)(Lpad / block), (unsigned)H);
   int8_t* o = static_cast<int8_t*>(out);
-#define KSB_LAUNCH_Q(T, B) prep::int8_block_quant_kernel<T, B><<<grid, prep::THREADS, 0, st>>>(static_cast<const T*>(x), L, token_stride, head_stride, premul, mean, o, scale, Lpad)
+#define KSB_LAUNCH_Q(T, B) prep::int8_block_quant_kernel<T, B><<<grid, B * 4, 0, st>>>(static_cast<const T*>(x), L, token_stride, head_stride, premul, mean, o, scale, Lpad)
   if (dtype == KSB_BF16) {
     if (block == 128) KSB_LAUNCH_Q(__nv_bfloat16, 128); else KSB_LAUNCH_Q(__nv_bfloat16, 64);
   } else {

@@ -301,7 +301,7 @@ def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean
     _lib.check(lib.ksb_rmsnorm_rope_inplace(_p(x), _dt(x), L, C, x.stride(0) if L > 1 else C, _p(w), int(per_head), float(eps), _p(tab),
                                             tlen, nf, nh, F, Hh, Ww, int(pos0), int(diag), _p(partial), _p(mean), _stream()),
                "ksb_rmsnorm_rope_inplace")
-    STATS.count(2 if want_mean else 1)
+    STATS.count(3 if want_mean else 1)
     return mean
 
 
