@@ -148,7 +148,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3+int8 (emulated in fp32)", "data": "synthetic",
-        "config": {"workload": "wan2.2-14b denoise step, 75600 tokens: CPU sample of one block", "sample_tokens": args.cpu_tokens},
+        "config": {"workload": f"wan2.2-14b denoise step: {W14['layers']} blocks, dim {W14['dim']}, {W14['heads']} heads x 128, "
+                               f"ffn {W14['ffn']}, 75600 tokens (grid {W14['grid']}), {W14['text_len']} text tokens, batch 1",
+                   "parallelism": "host cores", "sample": f"one block of that shape on {args.cpu_tokens} tokens per step"},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": vals[0][2]},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))

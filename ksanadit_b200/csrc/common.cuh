@@ -22,6 +22,7 @@ namespace ksb {
 enum StatusCode : int {
   KSB_OK = 0,
   KSB_ERR_WAIT_TIMEOUT = 1,  // detail = (kernel id << 16) | site
+  KSB_ERR_BAD_SMEM_ALIGNMENT = 2,
 };
 
 __device__ __forceinline__ void report_error(int* status, int code, int detail) {

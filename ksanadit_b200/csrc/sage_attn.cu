@@ -10,7 +10,7 @@
 // tiles; two CTAs share an SM (256 tensor-memory columns and ~98 KB of shared memory each), so one
 // CTA's softmax overlaps the other's MMAs.  Warp roles inside a CTA:
 //   warp 0      TMA producer (Q block once per work item; K and V^T tiles through 2-deep rings)
-//   warp 1      MMA issuer (single thread): S = Q.K^T for tile j+1 is queued before P.V of tile j
+//   warp 1      MMA issuer (single thread): S = Q.K^T for tile j+1 is queued before P.V of tile j; P alternates between two shared-memory buffers
 //   warps 2,3   idle (they only donate registers)
 //   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written to shared memory
 //               in the 128-byte-swizzled K-major layout the MMA reads, O rescaled in tensor memory in the
@@ -38,8 +38,12 @@ constexpr int KERNEL_ID = 2;
 constexpr uint32_t S_MAGIC_BITS = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23: one ulp is 1 on [2^23, 2^24)
 constexpr float S_MAGIC = 12582912.0f;
 constexpr float P_SHIFT = 8.0f;  // P carries a static factor 2^8 into e4m3: the row maximum maps to 256 exactly
-constexpr int NUM_BARS = 12;
-constexpr int SMEM_BYTES = 1024 + (2 + KST + VST) * TILE_BYTES + 8 * NUM_BARS + 64;
+constexpr int PST = 2;  // P buffers: P of tile g goes to buffer g & 1, so it never waits for the previous P.V
+constexpr int NUM_BARS = 16;
+// Q | P x PST | K x KST | V x VST | barriers.  The dynamic shared memory window itself must be 1024-byte aligned
+// (checked at kernel start): with two CTAs per SM there is no room for alignment slack.
+constexpr int NUM_TILES = 1 + PST + KST + VST;
+constexpr int SMEM_BYTES = NUM_TILES * TILE_BYTES + 8 * NUM_BARS + 64;
 
 struct Params {
   const float* qs;
@@ -147,19 +151,23 @@ __global__ void __launch_bounds__(THREADS, 2)
 sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t base = smem_u32(smem_raw);
+  uint8_t* gen = smem_raw;
   const uint32_t q_smem = base, p_smem = base + TILE_BYTES;
-  const uint32_t k_smem = base + 2 * TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
+  const uint32_t k_smem = base + (1 + PST) * TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
   const uint32_t bars = v_smem + VST * TILE_BYTES;
   const uint32_t q_full = bars, q_empty = bars + 8, k_full = bars + 16, k_empty = bars + 32, v_full = bars + 48,
-                 v_empty = bars + 64, s_full = bars + 80, s_empty = bars + 88, p_full = bars + 96, p_empty = bars + 104;
+                 v_empty = bars + 64, s_full = bars + 80, s_empty = bars + 88, p_full = bars + 96, p_empty = bars + 112;  // p_*: PST each
   const uint32_t tmem_slot = bars + 8 * NUM_BARS + 16;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + (2 + KST + VST) * TILE_BYTES + 8 * NUM_BARS + 16);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + NUM_TILES * TILE_BYTES + 8 * NUM_BARS + 16);
   uint8_t* p_gen = gen + TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total = p.H * p.nq;
+  if ((base & 1023u) != 0) {  // uniform over the CTA: the swizzled tiles need a 1024-byte aligned window
+    if (threadIdx.x == 0) report_error(p.status, KSB_ERR_BAD_SMEM_ALIGNMENT, (KERNEL_ID << 16) | 99);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -168,8 +176,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int s = 0; s < VST; ++s) { mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1); }
     mbar_init(s_full, 1);
     mbar_init(s_empty, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
-    mbar_init(p_full, 4);
-    mbar_init(p_empty, 1);
+    for (int b = 0; b < PST; ++b) { mbar_init(p_full + 8 * b, 4); mbar_init(p_empty + 8 * b, 1); }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -220,7 +227,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = IDESC_S8_S32(BQ, BKV);
       constexpr uint32_t idesc_pv = IDESC_F8_E4M3_F32(BQ, D);
-      const uint64_t dq = make_kmajor_sw128_desc(q_smem), dp = make_kmajor_sw128_desc(p_smem);
+      const uint64_t dq = make_kmajor_sw128_desc(q_smem);
       uint32_t wi = 0, itk = 0, itv = 0, g = 0;
       bool ok = true;
       auto issue_qk = [&](uint32_t gg) -> bool {
@@ -249,12 +256,14 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
           const uint32_t s = itv % VST, ph = (itv / VST) & 1;
           if (!mbar_wait(v_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 7)) { ok = false; break; }
-          if (!mbar_wait(p_full, g & 1, p.status, (KERNEL_ID << 16) | 8)) { ok = false; break; }
+          const uint32_t pb = g & 1, pph = (g >> 1) & 1;
+          if (!mbar_wait(p_full + 8 * pb, pph, p.status, (KERNEL_ID << 16) | 8)) { ok = false; break; }
+          const uint64_t dp = make_kmajor_sw128_desc(p_smem + pb * TILE_BYTES);
           tc_fence_after();
           const uint64_t dv = make_kmajor_sw128_desc(v_smem + s * TILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BKV / UMMA_K; ++kk) mma_f8_ss(tmem_o, dp + 2 * kk, dv + 2 * kk, idesc_pv, (j | kk) != 0);
-          mma_commit(p_empty);
+          mma_commit(p_empty + 8 * pb);
           mma_commit(v_empty + 8 * s);
           ++itv;
           ++g;
@@ -366,20 +375,22 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         exp_chunk(s[3], sc1, c1, pk + 24, acc);
         l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
         KSB_T(5);
-        // the previous P.V must have finished: it read the P buffer that is overwritten now and wrote the O
-        // accumulator that is rescaled below
-        if (!mbar_wait_warp(p_empty, (g & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
+        // this tile's P buffer was last read by the P.V of two tiles ago
+        const uint32_t pb = g & 1, pk_use = g >> 1;
+        if (!mbar_wait_warp(p_empty + 8 * pb, (pk_use & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
         KSB_T(6);
         // row `row` of the K-major tile: eight 16-byte chunks, chunk index XORed with (row & 7)
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const uint4 v4 = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-          *reinterpret_cast<uint4*>(p_gen + row * 128 + ((c ^ (row & 7)) << 4)) = v4;
+          *reinterpret_cast<uint4*>(p_gen + pb * TILE_BYTES + row * 128 + ((c ^ (row & 7)) << 4)) = v4;
         }
         fence_proxy_async_smem();
         KSB_T(7);
         if (rescale && j > 0) {
-          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now)
+          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now); the
+          // previous tile's P.V (the other P buffer) must have finished writing O
+          if (!mbar_wait_warp(p_empty + 8 * (pb ^ 1), ((g - 1) >> 1) & 1, p.status, (KERNEL_ID << 16) | 10)) { ok = false; break; }
           tc_fence_after();
           uint32_t o[4][32];
           tmem_ld32(tmem_o + lane_sel + 0, o[0]);
@@ -402,13 +413,13 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full);
+        if (lane == 0) mbar_arrive(p_full + 8 * pb);
         KSB_T(8);
         ++g;
       }
       if (!ok) break;
       // ---- epilogue of the work item: wait for the last P.V, normalise, store
-      if (!mbar_wait_warp(p_empty, (g & 1) ^ 1, p.status, (KERNEL_ID << 16) | 12)) { ok = false; break; }
+      if (!mbar_wait_warp(p_empty + 8 * ((g - 1) & 1), ((g - 1) >> 1) & 1, p.status, (KERNEL_ID << 16) | 12)) { ok = false; break; }
       tc_fence_after();
       const float inv_l = (l > 0.f) ? (1.f / l) : 0.f;
       const float* vsh = p.vs + w.h * D;
