@@ -184,6 +184,10 @@ def run_ours(args):
     flops = step_flops(cfg, L)
 
     model = B200WanDenoiseStep(cfg["layers"], cfg["dim"], cfg["ffn"], cfg["heads"], device=dev, seed=1000)
+    exchange = "none" if world == 1 else args.exchange
+    if exchange == "fused":
+        from ksanadit_b200.distribute import PeerExchange
+        model.use_peer_exchange(PeerExchange.symmetric(Ll, cfg["heads"], torch.bfloat16, dev))
     gh = torch.Generator().manual_seed(rank)
     # host-side inputs of a step (pinned): this rank's token shard, modulation, projected text context
     x_host = torch.empty(1, Ll, cfg["dim"], dtype=torch.bfloat16).pin_memory()
@@ -270,7 +274,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "fp8_e4m3+int8 (f32/s32 accumulate)", "data": "synthetic",
             "config": {"workload": f"wan2.2-14b denoise step: {cfg['layers']} blocks, dim {cfg['dim']}, {cfg['heads']} heads x 128, "
                                    f"ffn {cfg['ffn']}, {L} tokens (grid {cfg['grid']}), {cfg['text_len']} text tokens, batch 1",
-                       "parallelism": f"ulysses{world}", "tokens_per_rank": Ll,
+                       "parallelism": f"ulysses{world}", "tokens_per_rank": Ll, "exchange": exchange,
                        "l2": "inputs larger than L2: every kernel streams >= 387 MB per launch, no flush needed",
                        "step_pflop": flops / 1e15},
             "clocks": clocks,
@@ -303,6 +307,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="(profiling only) fewer blocks than the 40 of the headline workload")
     ap.add_argument("--grid", default="", help="(profiling only) FxHxW token grid instead of 21x45x80")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "fused"],
+                    help="Ulysses exchange at N > 1: NCCL all-to-alls, or peer stores fused into the GEMM / attention output stages")
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -31,6 +31,10 @@ extern "C" {
 #define KSB_EPI_NONE 0          /* out = acc*sa*sw + bias */
 #define KSB_EPI_GELU_TANH 1     /* out = gelu_tanh(round(acc*sa*sw + bias)) */
 #define KSB_EPI_GATE_RESIDUAL 2 /* out = resid + round(acc*sa*sw + bias) * gate */
+#define KSB_EPI_SCATTER_HEADS 3 /* only through ksb_fp8_gemm_qkv_scatter */
+
+/* most GPUs one exchange can span (the ranks of one NVLink / NVSwitch box) */
+#define KSB_MAX_PEERS 8
 
 /* token-block sizes of the INT8 scales and padding of the quantised attention operands */
 #define KSB_Q_BLOCK 128
@@ -91,6 +95,27 @@ int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, const float
                  int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo, int epilogue,
                  const void* resid, int64_t ldr, const void* gate, int64_t gate_rows, ksb_stream_t stream);
 
+/* Fused QKV projection + Ulysses "scatter heads, gather sequence" exchange (sequence parallelism over P GPUs
+ * of one box).  Replaces the fused QKV Linear (ksana/operations/fuse_qkv/fuse_qkv.py:226-233) followed by the three
+ * all_to_all(x, scatter_dim=2, gather_dim=1) of ksana/models/wan/wan_model.py:134-141 (ksana/utils/distribute.py:112-122):
+ * the GEMM epilogue stores each output element straight into the memory of the GPU that owns its head (plain
+ * peer stores over NVLink, no separate exchange kernel, no pack / unpack copies).
+ *   a [M, K] e4m3 (this rank's M tokens), w [3C, K] e4m3 (rows: Q | K | V), C = heads * 128, C % 256 == 0.
+ *   peer_out[p] (host array of n_peers device pointers, peer_out[rank] is this GPU's own): each a
+ *   [n_peers * M, 3, heads / n_peers, 128] half buffer; row (rank * M + m) receives this rank's token m.
+ *   tile_sumsq: fp32 scratch [2 * C / 256][M]; receives, per 256-column tile of the Q and K thirds, the sum of
+ *   squares of each output row (for the full-width RMSNorm that follows, see ksb_rowsumsq_to_rstd_scatter).
+ * The caller must synchronise the peers (all of them done with this call) before any of them reads its buffer. */
+int ksb_fp8_gemm_qkv_scatter(const void* a, const float* a_scale, const void* w, const float* w_scale, const void* bias,
+                             int64_t M, int64_t C, int64_t K, int dtype, void* const* peer_out, int n_peers, int rank,
+                             int64_t heads, float* tile_sumsq, ksb_stream_t stream);
+
+/* Turns the tile sums of squares above into rstd = rsqrt(sum / C + eps) per (Q | K, token) and stores them into
+ * every peer's fp32 [2, n_peers * M] table at column rank * M + m (what norm_q / norm_k,
+ * ksana/operations/ops.py:64-70, need once the heads of a token live on different GPUs). */
+int ksb_rowsumsq_to_rstd_scatter(const float* tile_sumsq, int64_t M, int64_t C, float eps, float* const* peer_rstd,
+                                 int n_peers, int rank, ksb_stream_t stream);
+
 /* Gated residual out = x + y * gate (one rounding), for the places where it is not fused into a GEMM
  * epilogue.  Replaces torch.addcmul(x, y, gate) / x + gate * y (wan_model.py:385,392;
  * ksana/models/qwen/transformer.py:225-234).  x, y, out: [M,N] half contiguous; gate: [gate_rows, N]. */
@@ -122,12 +147,14 @@ int ksb_sage_kmean(const void* k, int dtype, int64_t L, int64_t H, int64_t D, in
  * at position pos0 + l of an F x Hh x Ww grid (rows past the grid are not rotated).  The caller puts whatever
  * angle belongs to coordinate index r of each axis into row r (Wan: r * inv_freq; Qwen: centred positions).
  * diag == 1 (grid (F,1,1)): the running position drives all three axes (Qwen text tokens).
+ * row_rstd (optional, fp32 [L]): use these per-row factors instead of computing rsqrt(mean(x^2) + eps) over the C
+ * channels present (for rows whose other heads live on other GPUs; per_head must be 0).
  * rope_table NULL = no rotation.  colsum_partial (fp32 scratch, ksb_rmsnorm_rope_scratch_floats) with
  * colmean [C]: also returns the per-channel mean over the L rows of the values written (the K smoothing
  * vector, sage_sla.py:198); both NULL to skip. */
 int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C);
 int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, int per_head,
-                             float eps, const float* rope_table, int table_len, int nf, int nh, int F, int Hh,
+                             const float* row_rstd, float eps, const float* rope_table, int table_len, int nf, int nh, int F, int Hh,
                              int Ww, int64_t pos0, int diag, float* colsum_partial, float* colmean,
                              ksb_stream_t stream);
 
@@ -171,11 +198,15 @@ int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H,
  * kv_tile within a row.  NULL/NULL = dense.  A Q block with an empty list produces zeros.
  * q_order (optional, int32 [Lq_pad/128]): a permutation of the Q blocks; the CTAs walk the blocks of a head in
  * this order (pass the blocks sorted by decreasing list length to balance a ragged block-sparse mask over the
- * persistent CTAs).  NULL = ascending. */
+ * persistent CTAs).  NULL = ascending.
+ * peer_out / n_peers / rows_per_peer (optional; NULL / 0 / 0 = write to `out`): the Ulysses "scatter sequence,
+ * gather heads" exchange (ksana/models/wan/wan_model.py:143-146) fused into the output stage: output row l goes
+ * to peer_out[l / rows_per_peer] at row l % rows_per_peer, with the same strides as `out` (the caller offsets each
+ * peer pointer to this rank's head slot).  The peers must be synchronised before they read. */
 int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vs,
                   int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets, const int32_t* tile_entries,
                   const int32_t* q_order, void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride,
-                  ksb_stream_t stream);
+                  void* const* peer_out, int n_peers, int64_t rows_per_peer, ksb_stream_t stream);
 
 #ifdef __cplusplus
 }

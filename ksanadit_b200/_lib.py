@@ -33,7 +33,7 @@ SIGNATURES = {
     "ksb_sage_kmean_scratch_floats": (c_int64, [c_int64, c_int64, c_int64]),
     "ksb_sage_kmean": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ksb_rmsnorm_rope_scratch_floats": (c_int64, [c_int64, c_int64]),
-    "ksb_rmsnorm_rope_inplace": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_float, c_void_p, c_int,
+    "ksb_rmsnorm_rope_inplace": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
                                          c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "ksb_sage_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_void_p,
                                     c_void_p, c_void_p, c_void_p]),
@@ -42,7 +42,10 @@ SIGNATURES = {
     "ksb_sage_quant_v_fp8_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                              c_void_p]),
     "ksb_sage_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]),
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p]),
+    "ksb_fp8_gemm_qkv_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                         c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p]),
+    "ksb_rowsumsq_to_rstd_scatter": (c_int, [c_void_p, c_int64, c_int64, c_float, c_void_p, c_int, c_int, c_void_p]),
 }
 
 _lib = None

@@ -47,6 +47,13 @@ struct Params {
   const void* gate;
   int64_t gate_rows;
   int* status;
+  // KSB_EPI_SCATTER_HEADS (fused QKV projection + Ulysses exchange): the output row of local token m and
+  // column n = which * C + head * 128 + d goes to peer head / heads_per_peer, into its [tokens_all, 3, heads_per_peer,
+  // 128] buffer at token (rank * M + m); the sum of squares of every row of each 256-column tile is written to
+  // tile_sumsq[tile_n][m] for the tiles of the Q and K thirds.
+  void* peers[KSB_MAX_PEERS];
+  int n_peers, rank, heads_per_peer, C;
+  float* tile_sumsq;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
@@ -179,6 +186,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       T* orow = out + static_cast<int64_t>(row) * p.ldo + tn * BN;
       const T* rrow = p.resid ? static_cast<const T*>(p.resid) + static_cast<int64_t>(row) * p.ldr + tn * BN : nullptr;
       const T* grow = (p.gate && p.gate_rows != 1) ? static_cast<const T*>(p.gate) + static_cast<int64_t>(row) * p.N + tn * BN : nullptr;
+      const bool scatter = p.epilogue == KSB_EPI_SCATTER_HEADS;
+      float ssq = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -214,11 +223,27 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               T* ot = reinterpret_cast<T*>(&o);
 #pragma unroll
               for (int i = 0; i < 8; ++i) ot[i] = HalfOps<T>::from_f(y[i]);
-              *reinterpret_cast<uint4*>(orow + cb) = o;
+              if (scatter) {
+                // a 32-column chunk never straddles a head (128 columns) or a Q / K / V third (C % 256 == 0)
+                const int n = tn * BN + cb;
+                const int which = n / p.C, c = n - which * p.C;
+                const int head = c >> 7, dest = head / p.heads_per_peer, hl = head - dest * p.heads_per_peer;
+                T* dst = static_cast<T*>(p.peers[dest]) +
+                         ((static_cast<int64_t>(p.rank) * p.M + row) * 3 + which) * (static_cast<int64_t>(p.heads_per_peer) * 128) + hl * 128 + (c & 127);
+                *reinterpret_cast<uint4*>(dst) = o;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float v = HalfOps<T>::to_f(ot[i]);
+                  ssq = fmaf(v, v, ssq);
+                }
+              } else {
+                *reinterpret_cast<uint4*>(orow + cb) = o;
+              }
             }
           }
         }
       }
+      if (scatter && row_ok && p.tile_sumsq && tn * BN < 2 * p.C) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
@@ -238,6 +263,28 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 }  // namespace ksb
 
 using namespace ksb;
+
+static int launch_gemm(gemm::Params& p, const void* a, const void* w, int dtype, cudaStream_t st);
+
+extern "C" int ksb_fp8_gemm_qkv_scatter(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                                        const void* bias, int64_t M, int64_t C, int64_t K, int dtype, void* const* peer_out,
+                                        int n_peers, int rank, int64_t heads, float* tile_sumsq, ksb_stream_t stream) {
+  if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
+  if (M <= 0 || C <= 0 || K <= 0 || M > INT32_MAX / 4 || C > INT32_MAX / 4 || K > INT32_MAX) return fail(KSB_ERR_INVALID, "bad shape");
+  if (K % 16 != 0 || C % 256 != 0 || heads * 128 != C) return fail(KSB_ERR_INVALID, "need K %% 16 == 0, C %% 256 == 0 and C == heads * 128");
+  if (n_peers < 1 || n_peers > KSB_MAX_PEERS || rank < 0 || rank >= n_peers || heads % n_peers != 0)
+    return fail(KSB_ERR_INVALID, "n_peers must be 1..%d, rank inside it, heads divisible by it", KSB_MAX_PEERS);
+  if (!a || !a_scale || !w || !w_scale || !peer_out || !tile_sumsq) return fail(KSB_ERR_INVALID, "null pointer");
+  gemm::Params p{};
+  p.M = (int)M; p.N = (int)(3 * C); p.K = (int)K;
+  p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = peer_out[rank]; p.ldo = 3 * C; p.epilogue = KSB_EPI_SCATTER_HEADS;
+  for (int i = 0; i < n_peers; ++i) {
+    if (!peer_out[i] || !aligned16(peer_out[i])) return fail(KSB_ERR_INVALID, "peer buffer %d null or unaligned", i);
+    p.peers[i] = peer_out[i];
+  }
+  p.n_peers = n_peers; p.rank = rank; p.heads_per_peer = (int)(heads / n_peers); p.C = (int)C; p.tile_sumsq = tile_sumsq;
+  return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale,
                             const void* bias, int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo,
@@ -259,20 +306,24 @@ extern "C" int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, 
     resid = nullptr;
     gate = nullptr;
   }
-  CUtensorMap ta, tw;
-  if (int rc = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K, (uint64_t)M, (uint64_t)K, gemm::BK, gemm::BM)) return rc;
-  if (int rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, (uint64_t)K, (uint64_t)N, (uint64_t)K, gemm::BK, gemm::BN)) return rc;
   gemm::Params p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = out; p.ldo = ldo; p.epilogue = epilogue;
   p.resid = resid; p.ldr = ldr; p.gate = gate; p.gate_rows = gate_rows;
+  return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
+}
+
+static int launch_gemm(gemm::Params& p, const void* a, const void* w, int dtype, cudaStream_t st) {
+  const int64_t M = p.M, N = p.N, K = p.K;
+  CUtensorMap ta, tw;
+  if (int rc = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K, (uint64_t)M, (uint64_t)K, gemm::BK, gemm::BM)) return rc;
+  if (int rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, (uint64_t)K, (uint64_t)N, (uint64_t)K, gemm::BK, gemm::BN)) return rc;
   p.group_m = 64;
   while (p.group_m > 8 && (int64_t)p.group_m * gemm::BM * K > (32ll << 20)) p.group_m >>= 1;
   p.status = status_words();
   if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");
   const int tiles = (int)((M + gemm::BM - 1) / gemm::BM) * (int)((N + gemm::BN - 1) / gemm::BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == KSB_BF16) {
     if (cudaFuncSetAttribute(gemm::fp8_gemm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES) != cudaSuccess)
       return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");

@@ -56,6 +56,10 @@ struct Params {
   void* out;
   int64_t out_ts, out_hs;
   int* status;
+  // optional fused exchange: output row l goes to peers[l / rows_per_peer], row l % rows_per_peer
+  void* peers[KSB_MAX_PEERS];
+  int n_peers;
+  int rows_per_peer;
 };
 
 struct Work {
@@ -295,7 +299,13 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
       const Work w = get_work(p, idx);
       const int qrow = w.qt * BQ + row;
-      T* orow = out + static_cast<int64_t>(qrow) * p.out_ts + static_cast<int64_t>(w.h) * p.out_hs;
+      T* orow;
+      if (p.n_peers > 0) {
+        const int dest = min(qrow / p.rows_per_peer, p.n_peers - 1);  // rows past Lq are never stored
+        orow = static_cast<T*>(p.peers[dest]) + static_cast<int64_t>(qrow - dest * p.rows_per_peer) * p.out_ts + static_cast<int64_t>(w.h) * p.out_hs;
+      } else {
+        orow = out + static_cast<int64_t>(qrow) * p.out_ts + static_cast<int64_t>(w.h) * p.out_hs;
+      }
       if (w.n == 0) {
         if (qrow < p.Lq) {
 #pragma unroll
@@ -478,12 +488,21 @@ extern "C" int ksb_debug_attn_phase_cycles(unsigned long long* out16, int reset)
 extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
                              const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,
                              const int32_t* tile_entries, const int32_t* q_order, void* out, int dtype,
-                             int64_t out_token_stride, int64_t out_head_stride, ksb_stream_t stream) {
+                             int64_t out_token_stride, int64_t out_head_stride, void* const* peer_out, int n_peers,
+                             int64_t rows_per_peer, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (H <= 0 || Lq <= 0 || Lk <= 0) return fail(KSB_ERR_INVALID, "bad shape H=%lld Lq=%lld Lk=%lld", (long long)H, (long long)Lq, (long long)Lk);
-  if (!q8 || !qs || !k8 || !ks || !vt || !vs || !out) return fail(KSB_ERR_INVALID, "null pointer");
+  if (!q8 || !qs || !k8 || !ks || !vt || !vs || (!out && !peer_out)) return fail(KSB_ERR_INVALID, "null pointer");
+  if (peer_out) {
+    if (n_peers < 1 || n_peers > KSB_MAX_PEERS || rows_per_peer <= 0 || rows_per_peer * n_peers < Lq || rows_per_peer > INT32_MAX)
+      return fail(KSB_ERR_INVALID, "peer_out needs 1..%d peers and rows_per_peer * n_peers >= Lq", KSB_MAX_PEERS);
+    for (int i = 0; i < n_peers; ++i)
+      if (!peer_out[i] || !aligned16(peer_out[i])) return fail(KSB_ERR_INVALID, "peer buffer %d null or unaligned", i);
+  } else {
+    n_peers = 0;
+  }
   if ((tile_offsets == nullptr) != (tile_entries == nullptr)) return fail(KSB_ERR_INVALID, "tile_offsets and tile_entries must both be given or both be NULL");
-  if (!aligned16(out) || out_token_stride % 8 != 0 || out_head_stride % 8 != 0) return fail(KSB_ERR_INVALID, "out must be 16-byte aligned with strides multiple of 8 elements");
+  if ((out && !aligned16(out)) || out_token_stride % 8 != 0 || out_head_stride % 8 != 0) return fail(KSB_ERR_INVALID, "out must be 16-byte aligned with strides multiple of 8 elements");
   const int64_t nq = (Lq + 127) / 128, nkv = (Lk + 127) / 128;
   if (H * nq > INT32_MAX / 256 || H * nkv > INT32_MAX / 256) return fail(KSB_ERR_INVALID, "problem too large");
   CUtensorMap tq, tk, tv;
@@ -495,6 +514,8 @@ extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, co
   p.H = (int)H; p.Lq = (int)Lq; p.Lk = (int)Lk; p.nq = (int)nq; p.nkv = (int)nkv;
   p.offsets = tile_offsets; p.entries = tile_entries; p.order = q_order;
   p.out = out; p.out_ts = out_token_stride; p.out_hs = out_head_stride;
+  p.n_peers = n_peers; p.rows_per_peer = (int)rows_per_peer;
+  for (int i = 0; i < n_peers; ++i) p.peers[i] = peer_out[i];
   p.status = status_words();
   if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");
   const int64_t total = H * nq;

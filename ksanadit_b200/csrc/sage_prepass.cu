@@ -195,9 +195,28 @@ struct RopeGrid {
   int diag;      // 1: one running position drives all three axes (text tokens of the Qwen-Image block)
 };
 
+struct PeerTables {
+  float* p[KSB_MAX_PEERS];
+};
+
+// rstd[which][rank * M + m] = rsqrt(sum over the tiles of `which` of tile_sumsq[tile][m] / C + eps), written into
+// every peer's table (plain peer stores).
+__global__ void rstd_scatter_kernel(const float* __restrict__ tile_sumsq, int tiles_per_which, int M, int C, float eps,
+                                    PeerTables peers, int n_peers, int rank) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * M) return;
+  const int which = i / M, m = i - which * M;
+  float s = 0.f;
+  for (int t = 0; t < tiles_per_which; ++t) s += tile_sumsq[(int64_t)(which * tiles_per_which + t) * M + m];
+  const float r = rsqrtf(s / (float)C + eps);
+  const int64_t L_all = (int64_t)n_peers * M;
+  for (int d = 0; d < n_peers; ++d) peers.p[d][which * L_all + (int64_t)rank * M + m] = r;
+}
+
 template <typename T, bool ROPE, bool PER_HEAD, int NV>
 __global__ void __launch_bounds__(NR_THREADS, 4) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
-                                                                     const float* __restrict__ w, float eps, RopeGrid rg) {
+                                                                     const float* __restrict__ w, float eps, RopeGrid rg,
+                                                                     const float* __restrict__ row_rstd) {
   __shared__ float red[2][NR_THREADS / 32];
   const int nvec = C / 8;
   int par = 0;
@@ -225,6 +244,10 @@ __global__ void __launch_bounds__(NR_THREADS, 4) rmsnorm_rope_kernel(T* __restri
         for (int o = 8; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
         rstd_v[i] = rsqrtf(hs / (float)D + eps);
       }
+    } else if (row_rstd) {
+      const float r = row_rstd[l];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) rstd_v[i] = r;
     } else {
       float ss = 0.f;
 #pragma unroll
@@ -361,13 +384,28 @@ int64_t ksb_rmsnorm_rope_scratch_floats(int64_t L, int64_t C) {
   return ((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK) * C;
 }
 
-int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, int per_head, float eps,
-                             const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
+int ksb_rowsumsq_to_rstd_scatter(const float* tile_sumsq, int64_t M, int64_t C, float eps, float* const* peer_rstd,
+                                 int n_peers, int rank, ksb_stream_t stream) {
+  if (!tile_sumsq || !peer_rstd || M <= 0 || C <= 0 || C % 256 != 0) return fail(KSB_ERR_INVALID, "bad arguments");
+  if (n_peers < 1 || n_peers > KSB_MAX_PEERS || rank < 0 || rank >= n_peers) return fail(KSB_ERR_INVALID, "bad peer count / rank");
+  prep::PeerTables pt{};
+  for (int i = 0; i < n_peers; ++i) {
+    if (!peer_rstd[i]) return fail(KSB_ERR_INVALID, "peer table %d is null", i);
+    pt.p[i] = peer_rstd[i];
+  }
+  const int n = (int)(2 * M);
+  prep::rstd_scatter_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tile_sumsq, (int)(C / 256), (int)M, (int)C, eps, pt, n_peers, rank);
+  return check_launch("rstd scatter");
+}
+
+int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t ld, const float* w, int per_head,
+                             const float* row_rstd, float eps, const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
                              int diag, float* colsum_partial, float* colmean, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (L <= 0 || C <= 0 || C % 128 != 0 || C > prep::NR_THREADS * 8 * prep::NR_MAX_VEC) return fail(KSB_ERR_INVALID, "C=%lld must be a multiple of 128 and <= 8192", (long long)C);
   if (!x || !w || !aligned16(x) || !aligned16(w) || ld < C || ld % 8 != 0) return fail(KSB_ERR_INVALID, "x/w null, unaligned or bad row stride");
   if ((colsum_partial == nullptr) != (colmean == nullptr)) return fail(KSB_ERR_INVALID, "colsum_partial and colmean go together");
+  if (row_rstd && per_head) return fail(KSB_ERR_INVALID, "row_rstd and per_head exclude each other");
   prep::RopeGrid rg{};
   if (rope_table) {
     if (nf < 0 || nh < 0 || nf + nh > 64 || F <= 0 || Hh <= 0 || Ww <= 0) return fail(KSB_ERR_INVALID, "bad rope grid");
@@ -380,7 +418,7 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
   const int64_t cap = (int64_t)sm_count() * 16;
   const int blocks = (int)(L < cap ? L : cap);
   const bool wide = C > prep::NR_THREADS * 8 * 4;  // more than 4 vectors per thread
-#define KSB_LAUNCH_NR(T, R, P, NV) prep::rmsnorm_rope_kernel<T, R, P, NV><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg)
+#define KSB_LAUNCH_NR(T, R, P, NV) prep::rmsnorm_rope_kernel<T, R, P, NV><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg, row_rstd)
 #define KSB_LAUNCH_NR3(T, R, P) do { if (wide) KSB_LAUNCH_NR(T, R, P, 8); else KSB_LAUNCH_NR(T, R, P, 4); } while (0)
 #define KSB_LAUNCH_NR2(T)                                                          \
   do {                                                                             \

@@ -75,3 +75,73 @@ def gather_forward(input: torch.Tensor, dim: int) -> torch.Tensor:  # noqa: A002
     if get_world_size() == 1:
         return input
     return torch.cat(all_gather(input), dim=dim).contiguous()
+
+
+# ----------------------------------------------------------------------------- fused exchange over peer memory
+
+class PeerExchange:
+    """Buffers of one rank for the exchange fused into the GEMM / attention epilogues (plain peer stores over
+    NVLink instead of the two all-to-alls of wan_model.py:134-146).
+
+      qkv  [P*L_loc, 3, H/P, 128]  every rank's QKV GEMM stores its token rows of this rank's heads here
+      rstd [2, P*L_loc] fp32       norm_q / norm_k factors of all tokens (every rank stores its own columns)
+      out  [L_loc, H, 128]         every rank's attention kernel stores this rank's token rows of its heads here
+
+    ``*_ptrs`` hold the device addresses of the same buffer on every rank, indexed by rank.  ``barrier()`` must
+    order "all ranks have finished storing" before "any rank reads" on the current stream.
+    """
+
+    def __init__(self, P, rank, L_loc, heads, dtype, device, qkv, rstd, out, qkv_ptrs, rstd_ptrs, out_ptrs, barrier):
+        self.P, self.rank, self.L_loc, self.heads, self.dtype, self.device = P, rank, L_loc, heads, dtype, device
+        self.qkv, self.rstd, self.out = qkv, rstd, out
+        self.qkv_ptrs, self.rstd_ptrs, self.out_ptrs = list(qkv_ptrs), list(rstd_ptrs), list(out_ptrs)
+        self.barrier = barrier
+        C = heads * 128
+        self.tile_sumsq = torch.empty(2 * (C // 256), L_loc, dtype=torch.float32, device=device)
+
+    @staticmethod
+    def shapes(P, L_loc, heads):
+        return (P * L_loc, 3, heads // P, 128), (2, P * L_loc), (L_loc, heads, 128)
+
+    @classmethod
+    def local_group(cls, P, L_loc, heads, dtype, device):
+        """P contexts whose "peers" all live on one GPU: the layouts and kernels of the fused path without a second
+        GPU (the caller runs each phase for every virtual rank in turn; barrier is a no-op)."""
+        s_qkv, s_rstd, s_out = cls.shapes(P, L_loc, heads)
+        qkv = [torch.empty(s_qkv, dtype=dtype, device=device) for _ in range(P)]
+        rstd = [torch.empty(s_rstd, dtype=torch.float32, device=device) for _ in range(P)]
+        out = [torch.empty(s_out, dtype=dtype, device=device) for _ in range(P)]
+        return [cls(P, r, L_loc, heads, dtype, device, qkv[r], rstd[r], out[r], [t.data_ptr() for t in qkv],
+                    [t.data_ptr() for t in rstd], [t.data_ptr() for t in out], lambda: None) for r in range(P)]
+
+    @classmethod
+    def symmetric(cls, L_loc, heads, dtype, device, group=None):
+        """Buffers in torch's symmetric memory (one allocation per rank, mapped into every peer of the box).
+
+        Raises KsanaB200Error when symmetric memory cannot be set up; the NCCL all-to-all path stays available."""
+        import os
+
+        from . import _lib
+        # the in-switch reduction objects are not needed for plain peer stores; keep the buffers unbound from them
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_" + "MULTI" + "CAST", "1")
+        try:
+            import torch.distributed._symmetric_memory as symm
+        except Exception as e:  # pragma: no cover
+            raise _lib.KsanaB200Error(f"torch symmetric memory is unavailable: {e}") from e
+        P, rank = dist.get_world_size(group), dist.get_rank(group)
+        if P > 8:
+            raise _lib.KsanaB200Error("the fused exchange spans at most the 8 GPUs of one box")
+        gname = (group or dist.group.WORLD).group_name
+        bufs, ptrs = [], []
+        for shape, dt in zip(cls.shapes(P, L_loc, heads), (dtype, torch.float32, dtype)):
+            t = symm.empty(shape, dtype=dt, device=device)
+            h = symm.rendezvous(t, gname)
+            bufs.append(t)
+            ptrs.append([int(v) for v in h.buffer_ptrs])
+        flag = torch.zeros(1, dtype=torch.float32, device=device)
+
+        def barrier():
+            # stream-ordered: the stores of earlier kernels on this stream are complete before the collective runs
+            dist.all_reduce(flag, group=group)
+
+        return cls(P, rank, L_loc, heads, dtype, device, bufs[0], bufs[1], bufs[2], ptrs[0], ptrs[1], ptrs[2], barrier)

@@ -162,6 +162,41 @@ def fp8_gemm(a_q, a_scale, w_q, w_scale, bias=None, out_dtype=torch.bfloat16, ep
     return out
 
 
+def _ptr_array(ptrs):
+    """Host array of device pointers for the C ABI (kept alive by the caller for the duration of the call)."""
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*[int(v) for v in ptrs])
+
+
+def fp8_gemm_qkv_scatter(a_q, a_scale, w_q, w_scale, bias, heads, peer_ptrs, rank, tile_sumsq, dtype=torch.bfloat16):
+    """Fused QKV projection whose epilogue stores every element into the [P*M, 3, heads/P, 128] buffer of the GPU
+    that owns its head (``peer_ptrs``: device addresses of those buffers, own one included) and leaves per-tile
+    row sums of squares of the Q and K thirds in ``tile_sumsq`` ([2*C/256, M] fp32)."""
+    _cuda(a_q, a_scale, w_q, w_scale, bias, tile_sumsq)
+    M, K = a_q.shape
+    C = w_q.shape[0] // 3
+    assert w_q.shape == (3 * C, K) and a_q.is_contiguous() and w_q.is_contiguous() and C == heads * 128
+    assert tile_sumsq.dtype == torch.float32 and tile_sumsq.numel() >= 2 * (C // 256) * M and tile_sumsq.is_contiguous()
+    dt = _lib.BF16 if dtype == torch.bfloat16 else _lib.FP16
+    if bias is not None:
+        bias = bias.to(dtype).contiguous()
+    arr = _ptr_array(peer_ptrs)
+    STATS.timed(("gemm", M, 3 * C, K), lambda: _lib.check(
+        _lib.load().ksb_fp8_gemm_qkv_scatter(_p(a_q), _p(a_scale), _p(w_q), _p(w_scale), _p(bias), M, C, K, dt, arr, len(peer_ptrs),
+                                             int(rank), heads, _p(tile_sumsq), _stream()),
+        "ksb_fp8_gemm_qkv_scatter"))
+    STATS.count(1)
+
+
+def rowsumsq_to_rstd_scatter(tile_sumsq, M, C, eps, peer_ptrs, rank):
+    """rstd of the full-width RMSNorm of Q and K from the tile sums above, stored into every peer's [2, P*M] table."""
+    _cuda(tile_sumsq)
+    arr = _ptr_array(peer_ptrs)
+    _lib.check(_lib.load().ksb_rowsumsq_to_rstd_scatter(_p(tile_sumsq), M, C, float(eps), arr, len(peer_ptrs), int(rank), _stream()),
+               "ksb_rowsumsq_to_rstd_scatter")
+    STATS.count(1)
+
+
 def gate_residual(x, y, gate):
     _cuda(x, y, gate)
     M, N = x.shape
@@ -226,17 +261,32 @@ def q_premul(head_dim: int, sm_scale: float | None = None) -> float:
 
 
 def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, tile_offsets=None, tile_entries=None, out=None,
-                   tile_order=None):
-    """Quantised operands -> out [Lq, H, 128]."""
+                   tile_order=None, peer_out=None):
+    """Quantised operands -> out [Lq, H, 128].
+
+    peer_out = (ptrs, rows_per_peer, token_stride, head_stride): instead of ``out``, row l is stored at row
+    l % rows_per_peer of the buffer at ptrs[l // rows_per_peer] (device addresses, already offset to this rank's
+    head slot).  Returns None then."""
     _cuda(q8, qs, k8, ks, vt, vs, tile_offsets, tile_entries, tile_order, out)
     H = q8.shape[0]
+    if peer_out is not None:
+        ptrs, rows, ts, hs = peer_out
+        arr = _ptr_array(ptrs)
+        dt = _lib.BF16 if out_dtype == torch.bfloat16 else _lib.FP16
+        STATS.timed(("attn", H, Lq, Lk, tile_offsets is not None), lambda: _lib.check(
+            _lib.load().ksb_sage_attn(_p(q8), _p(qs), _p(k8), _p(ks), _p(vt), _p(vs), H, Lq, Lk, _p(tile_offsets),
+                                      _p(tile_entries), _p(tile_order), None, dt, ts, hs, arr, len(ptrs), rows, _stream()),
+            "ksb_sage_attn"))
+        STATS.count(1)
+        return None
     if out is None:
         out = torch.empty(Lq, H, 128, dtype=out_dtype, device=q8.device)
     assert out.stride(2) == 1
     dt = _lib.BF16 if out.dtype == torch.bfloat16 else _lib.FP16
     STATS.timed(("attn", H, Lq, Lk, tile_offsets is not None), lambda: _lib.check(
         _lib.load().ksb_sage_attn(_p(q8), _p(qs), _p(k8), _p(ks), _p(vt), _p(vs), H, Lq, Lk, _p(tile_offsets),
-                                  _p(tile_entries), _p(tile_order), _p(out), dt, out.stride(0), out.stride(1), _stream()),
+                                  _p(tile_entries), _p(tile_order), _p(out), dt, out.stride(0), out.stride(1), None, 0, 0,
+                                  _stream()),
         "ksb_sage_attn"))
     STATS.count(1)
     return out
@@ -277,14 +327,17 @@ def wan_rope_table(head_dim: int = 128, max_len: int = 1024, theta: float = 1000
     return _ROPE_TABLES[key]
 
 
-def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean=False, per_head=False, diag=False):
+def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean=False, per_head=False, diag=False,
+                         row_rstd=None):
     """x: [L, C] half view (row stride allowed), normalised (and rotated) in place.
 
     w: fp32 [C] (norm over all channels) or [128] with per_head (norm over each head's 128 channels).
     rope: (table [len,64,2] fp32, n_f, n_h) or None; grid: (F, H, W); diag: one position for all axes.
+    row_rstd: fp32 [L] factors to use instead of rsqrt(mean(x^2) + eps) over the C channels present.
     Returns the fp32 column mean [C] of the written values when want_mean.
     """
-    _cuda(x, w)
+    _cuda(x, w, row_rstd)
+    assert row_rstd is None or (row_rstd.dtype == torch.float32 and row_rstd.is_contiguous() and row_rstd.numel() == x.shape[0])
     assert x.dim() == 2 and x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous()
     L, C = x.shape
     assert w.numel() == (128 if per_head else C)
@@ -298,7 +351,8 @@ def rmsnorm_rope_inplace(x, w, eps=1e-6, rope=None, grid=None, pos0=0, want_mean
         tab, nf, nh = rope
         tlen = tab.shape[0]
         F, Hh, Ww = (int(v) for v in grid)
-    _lib.check(lib.ksb_rmsnorm_rope_inplace(_p(x), _dt(x), L, C, x.stride(0) if L > 1 else C, _p(w), int(per_head), float(eps), _p(tab),
+    _lib.check(lib.ksb_rmsnorm_rope_inplace(_p(x), _dt(x), L, C, x.stride(0) if L > 1 else C, _p(w), int(per_head), _p(row_rstd),
+                                            float(eps), _p(tab),
                                             tlen, nf, nh, F, Hh, Ww, int(pos0), int(diag), _p(partial), _p(mean), _stream()),
                "ksb_rmsnorm_rope_inplace")
     STATS.count(3 if want_mean else 1)

@@ -52,6 +52,7 @@ class B200WanBlock(torch.nn.Module):
         self.modulation = torch.nn.Parameter(torch.zeros(1, 6, dim, device=device, dtype=dtype), requires_grad=False)
         self.tile_lists = tile_lists  # (offsets, entries, order) for block-sparse self-attention, or None
         self.cache_context = cache_context  # keep the quantised context K/V across steps (off: recomputed every call)
+        self.peer_exchange = None  # distribute.PeerExchange: exchange fused into the kernels instead of NCCL all-to-alls
         self._ones = None
         self._ctx_cache = None
 
@@ -138,8 +139,47 @@ class B200WanBlock(torch.nn.Module):
         self._ctx_cache = (key, val)
         return val
 
+    # The sequence-parallel self-attention with the exchange fused into the kernels' output stages, in three
+    # phases separated by "all ranks are done storing" barriers (distribute.PeerExchange):
+    #   a: QKV GEMM storing into the head owners' buffers + the norm factors of this rank's tokens to every rank
+    #   b: norm / RoPE / quantisers on (all tokens, local heads), attention storing into the token owners' buffers
+    #   c: this rank's [L, C] attention output
+    def _fused_phase_a(self, ex, xq, sx):
+        sa = self.self_attn
+        ops.fp8_gemm_qkv_scatter(xq, sx, sa.qkv.weight.data, sa.qkv.weight_scale_vector(), sa.qkv.bias, self.num_heads,
+                                 ex.qkv_ptrs, ex.rank, ex.tile_sumsq, self.dtype)
+        ops.rowsumsq_to_rstd_scatter(ex.tile_sumsq, xq.shape[0], self.dim, self.eps, ex.rstd_ptrs, ex.rank)
+
+    def _fused_phase_b(self, ex, grid, rope):
+        sa = self.self_attn
+        Hl = self.num_heads // ex.P
+        Cl = Hl * HEAD
+        La = ex.P * ex.L_loc
+        w = slice(ex.rank * Cl, (ex.rank + 1) * Cl)
+        g = ex.qkv.view(La, 3, Cl)
+        km = ops.rmsnorm_rope_inplace(g[:, 1], sa.norm_k.weight[w], self.eps, rope, grid, want_mean=True, row_rstd=ex.rstd[1])
+        ops.rmsnorm_rope_inplace(g[:, 0], sa.norm_q.weight[w], self.eps, rope, grid, row_rstd=ex.rstd[0])
+        q3, k3, v3 = ex.qkv[:, 0], ex.qkv[:, 1], ex.qkv[:, 2]
+        q8, qs = ops.sage_quant_int8(q3, ops.Q_BLOCK, premul=ops.q_premul(HEAD))
+        k8, ks = ops.sage_quant_int8(k3, ops.K_BLOCK, mean=km.view(Hl, HEAD))
+        vt, vs = ops.sage_quant_v(v3)
+        offs, ents, order = self.tile_lists if self.tile_lists is not None else (None, None, None)
+        esz = ex.out.element_size()
+        ptrs = [p + ex.rank * Cl * esz for p in ex.out_ptrs]  # this rank's head slot in every token owner's buffer
+        ops.sage_attn_core(q8, qs, k8, ks, vt, vs, La, La, self.dtype, offs, ents, tile_order=order,
+                           peer_out=(ptrs, ex.L_loc, self.dim, HEAD))
+
     def _self_attention(self, xq, sx, L, grid, rope):
         C, H = self.dim, self.num_heads
+        ex = self.peer_exchange
+        if ex is not None:
+            if ex.L_loc != L or ex.heads != H or ex.dtype != self.dtype:
+                raise _lib.KsanaB200Error(f"peer exchange was built for {ex.L_loc} tokens x {ex.heads} heads, got {L} x {H}")
+            self._fused_phase_a(ex, xq, sx)
+            ex.barrier()
+            self._fused_phase_b(ex, grid, rope)
+            ex.barrier()
+            return ex.out.view(L, C)
         P, rank = distribute.get_world_size(), distribute.get_rank_id()
         sa = self.self_attn
         qkv = sa.qkv.forward_quantized(xq, sx, self.dtype)  # [L, 3C]
@@ -226,6 +266,12 @@ class B200WanDenoiseStep(torch.nn.Module):
                           cache_context=cache_context).random_init(seed + i)
              for i in range(num_layers)]
         )
+
+    def use_peer_exchange(self, ex):
+        """Route every block's Ulysses exchange through ``ex`` (distribute.PeerExchange; None = NCCL all-to-alls)."""
+        for blk in self.blocks:
+            blk.peer_exchange = ex
+        return self
 
     def forward(self, x, e, grid_sizes, context):
         for blk in self.blocks:

@@ -36,7 +36,7 @@ def test_no_cpu_fallback_and_argument_checks():
     assert lib.ksb_quant_fp8_rowwise(None, 0, 4, 24, 24, None, None, None) == -1
     assert b"multiple of 16" in lib.ksb_last_error()
     assert lib.ksb_fp8_gemm(None, None, None, None, None, 4, 8, 16, None, 0, 8, 0, None, 0, None, 0, None) == -1
-    assert lib.ksb_sage_attn(None, None, None, None, None, None, 1, 1, 1, None, None, None, None, 0, 128, 128, None) == -1
+    assert lib.ksb_sage_attn(None, None, None, None, None, None, 1, 1, 1, None, None, None, None, 0, 128, 128, None, 0, 0, None) == -1
     assert lib.ksb_sage_kmean_scratch_floats(75600, 40, 128) == 148 * 40 * 128
 
 
