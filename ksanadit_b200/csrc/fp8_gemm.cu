@@ -9,7 +9,9 @@
 //               descriptors into a tensor-memory accumulator; two accumulators (2 x 256 columns) alternate
 //               so the epilogue of tile i overlaps the main loop of tile i+1
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (one row per thread), apply scales / bias / fused
-//               GELU-tanh or gated residual, convert to half, store
+//               GELU-tanh or gated residual, convert to half, store.  The scatter epilogue (fused Ulysses
+//               exchange) stages 128-byte row pieces in shared memory and sends each with one bulk copy to the
+//               memory of the GPU that owns the head: NVLink carries 128-byte writes, not 16-byte ones
 // Tiles are visited in groups of `group_m` row-tiles (all column tiles of a group, row-tile fastest) so that
 // CTAs running at the same time share operand tiles in L2.  The weight is streamed from HBM once per group,
 // the group's activation rows stay in L2 while the group sweeps the columns: the host picks the group height so
@@ -30,8 +32,11 @@ constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BY
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID = 1;
-// dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers]
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256;
+// Output staging of the scatter epilogue: one 128-byte row piece per epilogue thread, rows 144 bytes apart (the
+// 16-byte skew keeps the 16-byte shared-memory stores of a quarter warp on distinct banks).
+constexpr int SCATTER_COLS = 64, SCATTER_ROW_BYTES = SCATTER_COLS * 2 + 16, SCATTER_BYTES = 128 * SCATTER_ROW_BYTES;
+// dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers][scatter staging]
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256 + SCATTER_BYTES;
 
 struct Params {
   int M, N, K;
@@ -65,6 +70,14 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tm = first_m + r % rows;
   tn = r / rows;
 }
+
+__device__ __forceinline__ void bulk_store_128(void* dst, uint32_t src_smem) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 128;" ::"l"(dst), "r"(src_smem) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_source_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh(u)) = x * sigmoid(2u),  u = sqrt(2/pi) (x + 0.044715 x^3)
@@ -158,6 +171,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const int et = threadIdx.x - 64;
+    uint8_t* stage_row = gen + STAGES * STAGE_BYTES + 3 * BN * 4 + 256 + et * SCATTER_ROW_BYTES;
     uint32_t tcount = 0;
     bool failed = false;
     T* out = static_cast<T*>(p.out);
@@ -194,6 +208,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tmem_ld32(t_row + c0, r);
         tmem_wait_ld();
         if (row_ok) {
+          // the staged row piece is rewritten every 64 columns: wait until the previous bulk copy has read it
+          if (scatter && (c0 & 32) == 0) bulk_wait_source_read();
 #pragma unroll
           for (int v8 = 0; v8 < 4; ++v8) {
             const int cb = c0 + v8 * 8;
@@ -224,13 +240,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 8; ++i) ot[i] = HalfOps<T>::from_f(y[i]);
               if (scatter) {
-                // a 32-column chunk never straddles a head (128 columns) or a Q / K / V third (C % 256 == 0)
-                const int n = tn * BN + cb;
-                const int which = n / p.C, c = n - which * p.C;
-                const int head = c >> 7, dest = head / p.heads_per_peer, hl = head - dest * p.heads_per_peer;
-                T* dst = static_cast<T*>(p.peers[dest]) +
-                         ((static_cast<int64_t>(p.rank) * p.M + row) * 3 + which) * (static_cast<int64_t>(p.heads_per_peer) * 128) + hl * 128 + (c & 127);
-                *reinterpret_cast<uint4*>(dst) = o;
+                *reinterpret_cast<uint4*>(stage_row + (cb & 63) * 2) = o;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   const float v = HalfOps<T>::to_f(ot[i]);
@@ -241,6 +251,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               }
             }
           }
+          if (scatter && (c0 & 32) != 0) {
+            // 64 columns staged: they never straddle a head (128 columns) or a Q / K / V third (C % 256 == 0)
+            const int n = tn * BN + c0 - 32;
+            const int which = n / p.C, c = n - which * p.C;
+            const int head = c >> 7, dest = head / p.heads_per_peer, hl = head - dest * p.heads_per_peer;
+            T* dst = static_cast<T*>(p.peers[dest]) +
+                     ((static_cast<int64_t>(p.rank) * p.M + row) * 3 + which) * (static_cast<int64_t>(p.heads_per_peer) * 128) + hl * 128 + (c & 127);
+            fence_async_proxy_smem();
+            bulk_store_128(dst, smem_u32(stage_row));
+          }
         }
       }
       if (scatter && row_ok && p.tile_sumsq && tn * BN < 2 * p.C) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
@@ -248,6 +268,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
     }
+    bulk_wait_all();  // no bulk copy of this thread may outlive the kernel's shared memory
   }
 
   // ------------------------------------------------------------------ common exit
