@@ -185,9 +185,17 @@ def run_ours(args):
 
     model = B200WanDenoiseStep(cfg["layers"], cfg["dim"], cfg["ffn"], cfg["heads"], device=dev, seed=1000)
     exchange = "none" if world == 1 else args.exchange
-    if exchange == "fused":
+    if exchange in ("auto", "fused"):
+        # peer stores fused into the GEMM / attention output stages; "auto" keeps the NCCL all-to-alls when the
+        # peer-mapped buffers cannot be set up on this box (every rank takes the same branch)
         from ksanadit_b200.distribute import PeerExchange
-        model.use_peer_exchange(PeerExchange.symmetric(Ll, cfg["heads"], torch.bfloat16, dev))
+        try:
+            model.use_peer_exchange(PeerExchange.symmetric(Ll, cfg["heads"], torch.bfloat16, dev))
+            exchange = "fused"
+        except _lib.KsanaB200Error as err:
+            if exchange == "fused":
+                raise
+            exchange = f"nccl (peer buffers unavailable: {err})"
     gh = torch.Generator().manual_seed(rank)
     # host-side inputs of a step (pinned): this rank's token shard, modulation, projected text context
     x_host = torch.empty(1, Ll, cfg["dim"], dtype=torch.bfloat16).pin_memory()
@@ -307,7 +315,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="(profiling only) fewer blocks than the 40 of the headline workload")
     ap.add_argument("--grid", default="", help="(profiling only) FxHxW token grid instead of 21x45x80")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "fused"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "fused"],
                     help="Ulysses exchange at N > 1: NCCL all-to-alls, or peer stores fused into the GEMM / attention output stages")
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
     args = ap.parse_args()

@@ -132,11 +132,21 @@ class PeerExchange:
         if P > 8:
             raise _lib.KsanaB200Error("the fused exchange spans at most the 8 GPUs of one box")
         gname = (group or dist.group.WORLD).group_name
-        bufs, ptrs = [], []
-        for shape, dt in zip(cls.shapes(P, L_loc, heads), (dtype, torch.float32, dtype)):
-            t = symm.empty(shape, dtype=dt, device=device)
+        # allocate first (local), agree that every rank could, and only then enter the collective rendezvous:
+        # a rank that failed alone would leave the others waiting there
+        bufs, err = [], None
+        try:
+            for shape, dt in zip(cls.shapes(P, L_loc, heads), (dtype, torch.float32, dtype)):
+                bufs.append(symm.empty(shape, dtype=dt, device=device))
+        except Exception as e:
+            err = e
+        ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) != 1:
+            raise _lib.KsanaB200Error(f"symmetric memory could not be allocated on every rank ({err or 'another rank failed'})")
+        ptrs = []
+        for t in bufs:
             h = symm.rendezvous(t, gname)
-            bufs.append(t)
             ptrs.append([int(v) for v in h.buffer_ptrs])
         flag = torch.zeros(1, dtype=torch.float32, device=device)
 
