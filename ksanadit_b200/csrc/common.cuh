@@ -228,6 +228,17 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Same descriptor without swizzle: core matrices of 8 rows x 16 bytes; `lbo` = byte distance between core matrices
+// along a row, `sbo` = byte distance between groups of 8 rows.
+__device__ __forceinline__ uint64_t make_noswizzle_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
 // Instruction descriptor (dense, no negate, both operands K-major).
 //   bits 4-5 accumulator format (1 = f32, 2 = s32); bits 7-9 A format; bits 10-12 B format
 //   bits 17-22 N >> 3; bits 24-28 M >> 4

@@ -15,8 +15,8 @@
 //   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written to shared memory
 //               in the 128-byte-swizzled K-major layout the MMA reads, O rescaled in tensor memory in the
 //               tiles where a row maximum of the warp grew; final normalisation and store
-// The s32 score accumulator is pre-loaded with 0x4B400000 before every S = Q.K^T and the MMA accumulates
-// on top of it: the bit pattern read back, taken as an fp32, is exactly 12582912 + S (|S| < 2^22), so the
+// The s32 score accumulator is pre-loaded with 0x4B400000 before every S = Q.K^T (tcgen05.cp copies of a constant
+// shared-memory block, queued by the MMA issuer in front of the MMAs) and the MMA accumulates on top of it: the bit pattern read back, taken as an fp32, is exactly 12582912 + S (|S| < 2^22), so the
 // scores need no integer-to-float conversion and X = fma(bits_as_float, scale, -12582912 * scale - m + 8).
 // Every mbarrier wait is bounded (see common.cuh).
 //
@@ -43,7 +43,8 @@ constexpr int NUM_BARS = 16;
 // Q | P x PST | K x KST | V x VST | barriers.  The dynamic shared memory window itself must be 1024-byte aligned
 // (checked at kernel start): with two CTAs per SM there is no room for alignment slack.
 constexpr int NUM_TILES = 1 + PST + KST + VST;
-constexpr int SMEM_BYTES = NUM_TILES * TILE_BYTES + 8 * NUM_BARS + 64;
+constexpr int CONST_BYTES = 512;  // S_MAGIC_BITS words the score-accumulator pre-load copies from
+constexpr int SMEM_BYTES = NUM_TILES * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS + 64;
 
 struct Params {
   const float* qs;
@@ -159,11 +160,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* gen = smem_raw;
   const uint32_t q_smem = base, p_smem = base + TILE_BYTES;
   const uint32_t k_smem = base + (1 + PST) * TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
-  const uint32_t bars = v_smem + VST * TILE_BYTES;
+  const uint32_t const_smem = v_smem + VST * TILE_BYTES;
+  const uint32_t bars = const_smem + CONST_BYTES;
   const uint32_t q_full = bars, q_empty = bars + 8, k_full = bars + 16, k_empty = bars + 32, v_full = bars + 48,
                  v_empty = bars + 64, s_full = bars + 80, s_empty = bars + 88, p_full = bars + 96, p_empty = bars + 112;  // p_*: PST each
   const uint32_t tmem_slot = bars + 8 * NUM_BARS + 16;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + NUM_TILES * TILE_BYTES + 8 * NUM_BARS + 16);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + NUM_TILES * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS + 16);
   uint8_t* p_gen = gen + TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,6 +184,10 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(s_empty, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
     for (int b = 0; b < PST; ++b) { mbar_init(p_full + 8 * b, 4); mbar_init(p_empty + 8 * b, 1); }
     fence_barrier_init();
+  }
+  if (threadIdx.x < CONST_BYTES / 4) {
+    reinterpret_cast<uint32_t*>(gen + NUM_TILES * TILE_BYTES)[threadIdx.x] = S_MAGIC_BITS;
+    fence_proxy_async_smem();  // read by the tensor-memory copy engine
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -232,14 +238,21 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       constexpr uint32_t idesc_qk = IDESC_S8_S32(BQ, BKV);
       constexpr uint32_t idesc_pv = IDESC_F8_E4M3_F32(BQ, D);
       const uint64_t dq = make_kmajor_sw128_desc(q_smem);
+      // constant block: every word is the same, so only the footprint of the descriptor matters -- two core
+      // matrices 128 B apart along a row, sixteen row groups 16 B apart, all inside the 512-byte block
+      const uint64_t dconst = make_noswizzle_desc(const_smem, 128, 16);
       uint32_t wi = 0, itk = 0, itv = 0, g = 0;
       bool ok = true;
       auto issue_qk = [&](uint32_t gg) -> bool {
         const uint32_t s = itk % KST, ph = (itk / KST) & 1;
         if (!mbar_wait(k_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 4)) return false;
-        if (!mbar_wait(s_empty, gg & 1, p.status, (KERNEL_ID << 16) | 5)) return false;  // S pre-loaded (completion #gg)
+        if (!mbar_wait(s_empty, gg & 1, p.status, (KERNEL_ID << 16) | 5)) return false;  // S read by the softmax warps (completion #gg)
         tc_fence_after();
         const uint64_t dk = make_kmajor_sw128_desc(k_smem + s * TILE_BYTES);
+        // pre-load the accumulator: 16 copies of 128 rows x 32 B, executed in order in front of the MMAs
+#pragma unroll
+        for (int c = 0; c < BKV; c += 8)
+          asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_s + c), "l"(dconst) : "memory");
 #pragma unroll
         for (int kk = 0; kk < D / UMMA_K; ++kk) mma_i8_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_qk, 1);  // on top of the pre-load
         mma_commit(s_full);
@@ -289,10 +302,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     long long ph_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     long long tprev_ = clock64();
 #endif
-    // pre-load the score accumulator for the first S = Q.K^T (completion #0 of s_empty)
-#pragma unroll
-    for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
-    tmem_wait_st();
+    // the score accumulator is free for the first S = Q.K^T (completion #0 of s_empty)
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(s_empty);
@@ -341,10 +351,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld32(tmem_s + lane_sel + 96, s[3]);
         tmem_wait_ld();
         KSB_T(2);
-        // pre-load the accumulator for the next S = Q.K^T, then hand it back to the MMA issuer
-#pragma unroll
-        for (int c = 0; c < BKV; c += 8) tmem_fill8(tmem_s + lane_sel + c, S_MAGIC_BITS);
-        tmem_wait_st();
+        // the scores are in registers: hand the accumulator back to the MMA issuer
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_empty);
@@ -379,22 +386,21 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t pk[32];
         float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         const float c0 = fmaf(-S_MAGIC, sc0, neg_m), c1 = fmaf(-S_MAGIC, sc1, neg_m);
-        exp_chunk(s[0], sc0, c0, pk, acc);
-        exp_chunk(s[1], sc0, c0, pk + 8, acc);
-        exp_chunk(s[2], sc1, c1, pk + 16, acc);
-        exp_chunk(s[3], sc1, c1, pk + 24, acc);
-        l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
-        KSB_T(5);
-        // this tile's P buffer was last read by the P.V of two tiles ago
+        // this tile's P buffer was last read by the P.V of two tiles ago; each 32-score chunk is stored as soon
+        // as it is packed (row `row` of the K-major tile: 16-byte chunks, chunk index XORed with (row & 7))
         const uint32_t pb = g & 1, pk_use = g >> 1;
         if (!mbar_wait_warp(p_empty + 8 * pb, (pk_use & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
         KSB_T(6);
-        // row `row` of the K-major tile: eight 16-byte chunks, chunk index XORed with (row & 7)
+        uint8_t* prow = p_gen + pb * TILE_BYTES + row * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v4 = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-          *reinterpret_cast<uint4*>(p_gen + pb * TILE_BYTES + row * 128 + ((c ^ (row & 7)) << 4)) = v4;
+        for (int h = 0; h < 4; ++h) {
+          exp_chunk(s[h], h < 2 ? sc0 : sc1, h < 2 ? c0 : c1, pk + 8 * h, acc);
+#pragma unroll
+          for (int c = 2 * h; c < 2 * h + 2; ++c)
+            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         }
+        l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+        KSB_T(5);
         fence_proxy_async_smem();
         KSB_T(7);
         if (rescale && j > 0) {
