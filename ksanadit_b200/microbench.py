@@ -135,10 +135,23 @@ def run_qwen(a):
                 t, i = b(i, t, temb, img_grid=grid)
         return i
 
-    t = timeit(step, a.iters, a.warmup)
     L = Li + Lt
     fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
-    print(f"qwen-image step: {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s ({fl / 1e15:.4f} PFLOP)")
+    t = timeit(step, a.iters, a.warmup)
+    print(f"qwen-image step, eager launches: {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s ({fl / 1e15:.4f} PFLOP)")
+    from .graph import StepGraph
+
+    def blocks_fn(i, t_, e):
+        for b in blocks:
+            t_, i = b(i, t_, e, img_grid=grid)
+        return i
+
+    g = StepGraph(blocks_fn, (img, txt, temb))
+    ref = step().float()
+    got = g(img, txt, temb).float()
+    print("  graph replay equals eager:", bool((ref == got).all()), f"({g.kernels_per_replay} kernels per replay)")
+    t = timeit(lambda: g(img, txt, temb), a.iters, a.warmup)
+    print(f"qwen-image step, one CUDA graph:  {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s")
 
 
 def main():

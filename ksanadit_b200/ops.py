@@ -367,6 +367,9 @@ def qwen_rope_tables(img_grid, txt_len, axes=(16, 56, 56), theta=10000.0, scale_
     row and of the r-th image column.  Text rows: row t holds the angles of position t0 + t on all three axes.
     """
     Fr, Hh, Ww = (int(v) for v in img_grid)
+    key = ("qwen", Fr, Hh, Ww, int(txt_len), tuple(axes), theta, scale_rope, str(device))
+    if key in _ROPE_TABLES:  # host-side set-up, cached per shape (also keeps the forward free of host->device copies)
+        return _ROPE_TABLES[key]
     inv = [1.0 / torch.pow(theta, torch.arange(0, d, 2, dtype=torch.float64) / d) for d in axes]
     n = max(Fr, Hh, Ww)
 
@@ -384,4 +387,5 @@ def qwen_rope_tables(img_grid, txt_len, axes=(16, 56, 56), theta=10000.0, scale_
     tpos = torch.arange(t0, t0 + txt_len, dtype=torch.float64)
     tang = torch.cat([torch.outer(tpos, i) for i in inv], dim=1)
     txt = torch.stack([torch.cos(tang), torch.sin(tang)], dim=-1).to(torch.float32).contiguous().to(device)
-    return (img, axes[0] // 2, axes[1] // 2), (txt, axes[0] // 2, axes[1] // 2)
+    _ROPE_TABLES[key] = ((img, axes[0] // 2, axes[1] // 2), (txt, axes[0] // 2, axes[1] // 2))
+    return _ROPE_TABLES[key]
