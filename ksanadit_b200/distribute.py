@@ -36,18 +36,34 @@ def all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, group=None, *
     return torch.cat(list(recv.unbind(0)), dim=gather_dim).contiguous()
 
 
-def heads_to_sequence(qkv: torch.Tensor, group=None) -> torch.Tensor:
+def heads_to_sequence(qkv: torch.Tensor, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
     """[L_loc, n, H, D] (n stacked tensors, all heads, local tokens) -> [L, n, H/P, D] (local heads, all tokens).
 
-    One all-to-all for q, k and v together (the reference does three, wan_model.py:138-140)."""
+    One all-to-all for q, k and v together (the reference does three, wan_model.py:138-140).  ``out``: a
+    contiguous [L, n, H/P, D] buffer to receive into (e.g. the image rows of a joint text+image buffer)."""
     P = get_world_size()
     if P == 1:
         return qkv
     Ll, n, H, D = qkv.shape
     send = qkv.view(Ll, n, P, H // P, D).permute(2, 0, 1, 3, 4).contiguous()  # [P, L_loc, n, H/P, D]
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.view(P * Ll, n, H // P, D)
+    if out is None:
+        out = torch.empty(P * Ll, n, H // P, D, dtype=qkv.dtype, device=qkv.device)
+    if out.shape != (P * Ll, n, H // P, D) or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {(P * Ll, n, H // P, D)} tensor")
+    dist.all_to_all_single(out.view(P, Ll, n, H // P, D), send, group=group)
+    return out
+
+
+def gather_heads(x: torch.Tensor, group=None) -> torch.Tensor:
+    """[L, H/P, D] (this rank's heads of a replicated sequence) -> [L, H, D]: the all_gather + cat over heads of
+    the replicated text stream (ksana/models/qwen/attention.py:298-307)."""
+    P = get_world_size()
+    if P == 1:
+        return x
+    L, Hl, D = x.shape
+    buf = torch.empty(P, L, Hl, D, dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(buf, x.contiguous(), group=group)
+    return buf.permute(1, 0, 2, 3).reshape(L, P * Hl, D)
 
 
 def sequence_to_heads(x: torch.Tensor, group=None) -> torch.Tensor:

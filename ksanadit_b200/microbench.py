@@ -119,11 +119,20 @@ def run_prepass(a):
 
 def run_qwen(a):
     """Qwen-Image-20B-shaped MMDiT step: 60 dual-stream blocks, dim 3072, 24 heads, 6889 image + 256 text tokens."""
+    import os
+
+    import torch.distributed as dist
+
     from .qwen_block import B200QwenBlock
     dim, heads, ffn, grid, Lt = 3072, 24, 12288, (1, 83, 83), 256
     layers = a.layers
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world > 1:  # launched by torch.distributed.run: image tokens sharded (padded to a multiple of the ranks)
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     blocks = [B200QwenBlock(dim, heads, ffn).random_init(100 + i) for i in range(layers)]
-    Li = grid[1] * grid[2]
+    Li_all = grid[1] * grid[2]
+    Li = (Li_all + world - 1) // world
     img = torch.randn(1, Li, dim, device="cuda").to(torch.bfloat16)
     txt = torch.randn(1, Lt, dim, device="cuda").to(torch.bfloat16)
     temb = torch.randn(1, dim, device="cuda").to(torch.bfloat16)
@@ -135,7 +144,17 @@ def run_qwen(a):
                 t, i = b(i, t, temb, img_grid=grid)
         return i
 
-    L = Li + Lt
+    L = Li_all + Lt
+    if world > 1:
+        t = timeit(step, a.iters, a.warmup)
+        tt = torch.tensor([t], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
+        if rank == 0:
+            print(f"qwen-image step on {world} GPUs (Ulysses, NCCL): {layers} blocks, {Li_all}+{Lt} tokens, {Li} image rows per rank: "
+                  f"{tt.item():.2f} ms  {fl / tt.item() / 1e9:.1f} TFLOP/s")
+        dist.destroy_process_group()
+        return
     fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
     t = timeit(step, a.iters, a.warmup)
     print(f"qwen-image step, eager launches: {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s ({fl / 1e15:.4f} PFLOP)")

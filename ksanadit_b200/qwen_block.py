@@ -10,15 +10,18 @@ Same parameters (state-dict names) and inputs as KsanaDiT's block
   per stream: quant -> out-projection GEMM (+ gated residual) -> adaLN+quant -> MLP up GEMM (+GELU-tanh) ->
               quant -> MLP down GEMM (+ gated residual)
 
-Single GPU only for now (the Ulysses variant replicates the text stream and slices its heads,
-qwen/attention.py:298-318; not built yet).
+Under Ulysses sequence parallelism (a process group is initialised) the image tokens are sharded over the ranks
+and the text stream is replicated, as in the reference (qwen/attention.py:283-318, 352-368): the per-head norm and
+RoPE run on the local image rows (global positions), one all-to-all brings this rank's heads of all image tokens
+next to its slice of the text heads, attention runs over the joint sequence for the local heads, the image rows
+go back by the reverse all-to-all and the text rows are all-gathered over heads.
 """
 
 from __future__ import annotations
 
 import torch
 
-from . import _lib, ops
+from . import _lib, distribute, ops
 from .linear import B200Fp8Linear, quantize_weight_per_channel
 
 HEAD = 128
@@ -114,8 +117,9 @@ class B200QwenBlock(torch.nn.Module):
         return mlp.net[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=gate2, out=x)
 
     def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, img_grid=None, **_):
-        """hidden_states [1, Li, C] (image), encoder_hidden_states [1, Lt, C] (text), temb [1, C];
-        img_grid (F, H, W) of the image tokens.  Returns (text, image) like the reference block.
+        """hidden_states [1, Li, C] (image; under sequence parallelism this rank's Li rows of the P * Li image
+        tokens, rows past the grid being padding), encoder_hidden_states [1, Lt, C] (text, replicated),
+        temb [1, C]; img_grid (F, H, W) of all image tokens.  Returns (text, image) like the reference block.
         ``image_rotary_emb`` is accepted for signature compatibility; the rotation tables are rebuilt from the
         same formula (QwenEmbedRope) for ``img_grid`` and the text length."""
         if hidden_states.shape[0] != 1:
@@ -123,27 +127,41 @@ class B200QwenBlock(torch.nn.Module):
         if img_grid is None:
             raise ValueError("img_grid=(F, H, W) is required")
         img, txt = hidden_states[0], encoder_hidden_states[0]
-        Li, C = img.shape
+        Li, C = img.shape  # local image rows
         Lt = txt.shape[0]
         H = self.num_heads
-        L = Lt + Li
+        P, rank = distribute.get_world_size(), distribute.get_rank_id()
+        if H % P != 0:
+            raise _lib.KsanaB200Error(f"{H} heads cannot be split over {P} ranks")
+        Hl = H // P
         img_tab, txt_tab = ops.qwen_rope_tables(img_grid, Lt, device=img.device)
         st = torch.nn.functional.silu(temb)
         imod = self.img_mod[1](st)[0].view(2, 3, 1, C)  # [mod1|mod2] x [shift|scale|gate]
         tmod = self.txt_mod[1](st)[0].view(2, 3, 1, C)
 
-        qkv = torch.empty(L, 3 * C, dtype=self.dtype, device=img.device)  # joint buffer, text rows first (attention.py:355-357)
+        # local projections: text rows first (attention.py:355-357), then this rank's image rows
+        qkv = torch.empty(Lt + Li, 3 * C, dtype=self.dtype, device=img.device)
         a = self.attn
-        for x, mod, lin, nq, nk, rows, tab, grid, diag in (
-            (txt, tmod, a.add_qkv_proj, a.norm_added_q, a.norm_added_k, slice(0, Lt), txt_tab, (Lt, 1, 1), True),
-            (img, imod, a.to_qkv, a.norm_q, a.norm_k, slice(Lt, L), img_tab, img_grid, False),
+        for x, mod, lin, nq, nk, rows, tab, grid, diag, pos0 in (
+            (txt, tmod, a.add_qkv_proj, a.norm_added_q, a.norm_added_k, slice(0, Lt), txt_tab, (Lt, 1, 1), True, 0),
+            (img, imod, a.to_qkv, a.norm_q, a.norm_k, slice(Lt, Lt + Li), img_tab, img_grid, False, rank * Li),
         ):
             xq, sx = ops.adaln_quant_fp8(x, mod[0, 0], mod[0, 1], self.eps, round_product=True)
             lin.forward_quantized(xq, sx, self.dtype, out=qkv[rows])
-            ops.rmsnorm_rope_inplace(qkv[rows, :C], nq.weight, self.eps, tab, grid, per_head=True, diag=diag)
-            ops.rmsnorm_rope_inplace(qkv[rows, C:2 * C], nk.weight, self.eps, tab, grid, per_head=True, diag=diag)
-        t = qkv.view(L, 3, H, HEAD)
-        o = ops.sage_attention(t[:, 0], t[:, 1], t[:, 2]).view(L, C)
-        txt = self._stream_tail(txt, o[:Lt], tmod[0, 2], tmod[1], a.to_add_out, self.txt_mlp)
-        img = self._stream_tail(img, o[Lt:], imod[0, 2], imod[1], a.to_out[0], self.img_mlp)
+            ops.rmsnorm_rope_inplace(qkv[rows, :C], nq.weight, self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
+            ops.rmsnorm_rope_inplace(qkv[rows, C:2 * C], nk.weight, self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
+        if P == 1:
+            t = qkv.view(Lt + Li, 3, H, HEAD)
+            o = ops.sage_attention(t[:, 0], t[:, 1], t[:, 2]).view(Lt + Li, C)
+            o_txt, o_img = o[:Lt], o[Lt:]
+        else:
+            # joint [text; all image tokens] x this rank's heads
+            joint = torch.empty(Lt + P * Li, 3, Hl, HEAD, dtype=self.dtype, device=img.device)
+            joint[:Lt] = qkv[:Lt].view(Lt, 3, H, HEAD)[:, :, rank * Hl:(rank + 1) * Hl]
+            distribute.heads_to_sequence(qkv[Lt:].view(Li, 3, H, HEAD), out=joint[Lt:])
+            o = ops.sage_attention(joint[:, 0], joint[:, 1], joint[:, 2])  # [Lt + P*Li, Hl, D]
+            o_txt = distribute.gather_heads(o[:Lt]).reshape(Lt, C)
+            o_img = distribute.sequence_to_heads(o[Lt:]).reshape(Li, C)
+        txt = self._stream_tail(txt, o_txt, tmod[0, 2], tmod[1], a.to_add_out, self.txt_mlp)
+        img = self._stream_tail(img, o_img, imod[0, 2], imod[1], a.to_out[0], self.img_mlp)
         return txt.unsqueeze(0), img.unsqueeze(0)

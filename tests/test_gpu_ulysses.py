@@ -96,3 +96,56 @@ def test_wan_block_two_ranks_match_one(tmp_path, mode):
     got = torch.cat([torch.load(tmp_path / f"y{r}.pt") for r in range(2)], dim=1).float()
     # the K-smoothing mean is an fp32 reduction whose order differs between the two paths
     assert cosine(got, ref) >= 0.9999 and max_abs_rel(got, ref) <= 1e-2
+
+
+_QWEN_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from ksanadit_b200.qwen_block import B200QwenBlock
+from ksanadit_b200 import _lib
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+dim, heads, ffn, grid, Lt = 512, 4, 1024, (1, 8, 12), 40
+blk = B200QwenBlock(dim, heads, ffn).random_init(9)
+g = torch.Generator().manual_seed(4)
+img = torch.randn(1, grid[1] * grid[2], dim, generator=g).to(torch.bfloat16)
+txt = torch.randn(1, Lt, dim, generator=g).to(torch.bfloat16)
+temb = torch.randn(1, dim, generator=g).to(torch.bfloat16)
+with torch.no_grad():
+    t, i = blk(img.chunk(world, dim=1)[rank].cuda(), txt.cuda(), temb.cuda(), img_grid=grid)
+_lib.assert_device_ok()
+torch.save((t.cpu(), i.cpu()), os.path.join(sys.argv[2], f"q{rank}.pt"))
+dist.barrier(); dist.destroy_process_group()
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_qwen_block_two_ranks_match_one(tmp_path):
+    """Image tokens sharded, text stream replicated with its heads sliced (qwen/attention.py:283-318)."""
+    from ksanadit_b200.qwen_block import B200QwenBlock
+    script = tmp_path / "qworker.py"
+    script.write_text(_QWEN_WORKER)
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29537",
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script), ROOT, str(tmp_path)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT))
+    for p in procs:
+        out, _ = p.communicate(timeout=600)
+        assert p.returncode == 0, out.decode()[-3000:]
+    dim, heads, ffn, grid, Lt = 512, 4, 1024, (1, 8, 12), 40
+    blk = B200QwenBlock(dim, heads, ffn).random_init(9)
+    g = torch.Generator().manual_seed(4)
+    img = torch.randn(1, grid[1] * grid[2], dim, generator=g).to(torch.bfloat16)
+    txt = torch.randn(1, Lt, dim, generator=g).to(torch.bfloat16)
+    temb = torch.randn(1, dim, generator=g).to(torch.bfloat16)
+    with torch.no_grad():
+        t_ref, i_ref = blk(img.cuda(), txt.cuda(), temb.cuda(), img_grid=grid)
+    parts = [torch.load(tmp_path / f"q{r}.pt") for r in range(2)]
+    i_got = torch.cat([p[1] for p in parts], dim=1).float()
+    # every rank computes the replicated text stream; both copies must agree with the one-rank result
+    for p in parts:
+        assert cosine(p[0].float(), t_ref.cpu().float()) >= 0.9999 and max_abs_rel(p[0].float(), t_ref.cpu().float()) <= 1e-2
+    assert cosine(i_got, i_ref.cpu().float()) >= 0.9999 and max_abs_rel(i_got, i_ref.cpu().float()) <= 1e-2
