@@ -245,13 +245,223 @@ __global__ void __launch_bounds__(THREADS, 4) rowwise_kernel(const Params p) {
   }
 }
 
+// Pair conversions: two fp32 values <-> one packed word of two halves (one conversion instruction per pair).
+template <typename T> struct Pair;
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t pack(float2 v) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+};
+template <> struct Pair<__half> {
+  static __device__ __forceinline__ uint32_t pack(float2 v) {
+    __half2 h = __floats2half2_rn(v.x, v.y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+};
+template <typename T> __device__ __forceinline__ float2 round_half2(float2 v) { return Pair<T>::unpack(Pair<T>::pack(v)); }
+// Pair arithmetic, written as two scalar instructions: the packed fp32x2 forms were measured here and bring
+// nothing (same instruction count and time; the values do not sit in aligned register pairs) and make the
+// affine-LayerNorm variant spill.
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
+
+// Rows of up to 48 (NC = 3: six CTAs per SM) or 64 (NC = 4: four) elements per thread: the thread's part of the row is unpacked to fp32
+// once and stays in fp32 registers through the statistics, the modulation, the absmax and the quantiser
+// (two-at-a-time conversions between halves and fp32).  The fused LayerNorm variants are bound by instruction
+// issue (66 % issue-active, ALU pipe 55 %: the half <-> fp32 conversions) as much as by HBM; every pass
+// re-unpacking packed registers cost a quarter more.  Rounding points are unchanged.
+template <typename T, int MODE, int WPR, int NC>
+__global__ void __launch_bounds__(THREADS, NC == 3 ? 6 : 4) rowwise_f32_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float red[3][2][4];
+  constexpr int RPC = 4 / WPR;          // rows per CTA per iteration
+  constexpr int GT = WPR * 32;          // threads per row
+  const int warp = threadIdx.x >> 5;
+  const int rg = warp / WPR;            // row slot of this warp
+  const int t = threadIdx.x - rg * GT;  // thread index inside the row group
+  const int nchunks = static_cast<int>(p.K / CHUNK);
+  const T* x = static_cast<const T*>(p.x);
+  const bool staged = (MODE == ADALN && p.mod_rows == 1) || MODE == LN_AFFINE;
+  // Staged vectors (adaLN: 1 + scale rounded to half, and shift; affine LN: weight and bias) are kept as units of
+  // 4 elements in unit-major order (unit u of chunk ch at index u * nchunks + ch): consecutive threads own
+  // consecutive chunks and read consecutive units, no bank conflicts.
+  // adaLN keeps them as halves (8-byte units of 4), affine LN as fp32 (16-byte units of 4).
+  float4* s_mul = reinterpret_cast<float4*>(smem);  // LN_AFFINE: [4][nchunks] float4
+  float4* s_add = s_mul + 4 * nchunks;
+  uint2* h_mul = reinterpret_cast<uint2*>(smem);    // ADALN: [4][nchunks] uint2
+  uint2* h_add = h_mul + 4 * nchunks;
+  if (staged) {
+    for (int i = threadIdx.x; i < 4 * nchunks; i += THREADS) {
+      const int ch = i >> 2, u = i & 3;
+      if (MODE == ADALN) {
+        const uint2 cw = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.scale) + ch * CHUNK + u * 4);
+        const float2 one = make_float2(1.f, 1.f);
+        uint2 m;  // (1 + scale) in half
+        m.x = Pair<T>::pack(add2(one, Pair<T>::unpack(cw.x)));
+        m.y = Pair<T>::pack(add2(one, Pair<T>::unpack(cw.y)));
+        h_mul[u * nchunks + ch] = m;
+        h_add[u * nchunks + ch] = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.shift) + ch * CHUNK + u * 4);
+      } else {
+        s_mul[u * nchunks + ch] = *reinterpret_cast<const float4*>(p.w + ch * CHUNK + u * 4);
+        s_add[u * nchunks + ch] = p.b ? *reinterpret_cast<const float4*>(p.b + ch * CHUNK + u * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    __syncthreads();
+  }
+  int par = 0;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * RPC; base < p.M; base += static_cast<int64_t>(gridDim.x) * RPC, par ^= 1) {
+    const int64_t row = base + rg;
+    const bool live = row < p.M;
+    float f[NC][16];
+    const T* xr = x + row * p.ldx;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int ch = t + c * GT;
+      uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+      if (live && ch < nchunks) {
+        a = *reinterpret_cast<const uint4*>(xr + ch * CHUNK);
+        b = *reinterpret_cast<const uint4*>(xr + ch * CHUNK + 8);
+      }
+      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 v = Pair<T>::unpack(w[i]);
+        f[c][2 * i] = v.x;
+        f[c][2 * i + 1] = v.y;
+      }
+    }
+    if (MODE == ADALN || MODE == LN_AFFINE) {
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) acc = add2(acc, make_float2(f[c][i], f[c][i + 1]));
+      const float mean = row_reduce<WPR, false>(acc.x + acc.y, &red[0][0][0], par, warp) / static_cast<float>(p.K);
+      const float2 nm2 = make_float2(-mean, -mean);
+      acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        if (t + c * GT < nchunks) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float2 d = add2(make_float2(f[c][i], f[c][i + 1]), nm2);
+            acc = fma2(d, d, acc);
+          }
+        }
+      }
+      const float var = row_reduce<WPR, false>(acc.x + acc.y, &red[1][0][0], par, warp) / static_cast<float>(p.K);
+      const float rstd = rsqrtf(var + p.eps);
+      const float2 r2 = make_float2(rstd, rstd);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int ch = t + c * GT;
+        if (live && ch < nchunks) {
+          uint32_t hw[8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float4 mu, ad;
+            if (staged && MODE == LN_AFFINE) {
+              mu = s_mul[u * nchunks + ch];
+              ad = s_add[u * nchunks + ch];
+            } else if (staged) {
+              const uint2 mw = h_mul[u * nchunks + ch], aw = h_add[u * nchunks + ch];
+              const float2 m01 = Pair<T>::unpack(mw.x), m23 = Pair<T>::unpack(mw.y), a01 = Pair<T>::unpack(aw.x), a23 = Pair<T>::unpack(aw.y);
+              mu = make_float4(m01.x, m01.y, m23.x, m23.y);
+              ad = make_float4(a01.x, a01.y, a23.x, a23.y);
+            } else {  // per-row modulation (ADALN only)
+              const T* gc = static_cast<const T*>(p.scale) + row * p.K + ch * CHUNK + u * 4;
+              const T* gs = static_cast<const T*>(p.shift) + row * p.K + ch * CHUNK + u * 4;
+              const uint2 cw = *reinterpret_cast<const uint2*>(gc), sw = *reinterpret_cast<const uint2*>(gs);
+              const float2 c01 = Pair<T>::unpack(cw.x), c23 = Pair<T>::unpack(cw.y), s01 = Pair<T>::unpack(sw.x), s23 = Pair<T>::unpack(sw.y);
+              const float2 one = make_float2(1.f, 1.f);
+              const float2 t01 = round_half2<T>(add2(one, c01)), t23 = round_half2<T>(add2(one, c23));  // (1 + scale) in half
+              mu = make_float4(t01.x, t01.y, t23.x, t23.y);
+              ad = make_float4(s01.x, s01.y, s23.x, s23.y);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int i = 4 * u + 2 * j;
+              const float2 m2 = j ? make_float2(mu.z, mu.w) : make_float2(mu.x, mu.y);
+              const float2 a2 = j ? make_float2(ad.z, ad.w) : make_float2(ad.x, ad.y);
+              float2 ln = mul2(add2(make_float2(f[c][i], f[c][i + 1]), nm2), r2);
+              float2 v;
+              if (MODE == ADALN) {
+                ln = round_half2<T>(ln);  // F.layer_norm output in half
+                v = p.round_product ? add2(round_half2<T>(mul2(ln, m2)), a2) : fma2(ln, m2, a2);
+              } else {
+                v = fma2(ln, m2, a2);
+              }
+              hw[2 * u + j] = Pair<T>::pack(v);  // the transformed row in half: what is quantised (and optionally stored)
+              const float2 vr = Pair<T>::unpack(hw[2 * u + j]);
+              f[c][i] = vr.x;
+              f[c][i + 1] = vr.y;
+            }
+          }
+          if (p.h_out) {
+            T* ho = static_cast<T*>(p.h_out) + row * p.K + ch * CHUNK;
+            *reinterpret_cast<uint4*>(ho) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4*>(ho + 8) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+          }
+        }
+      }
+    }
+    float inv_h;  // multiplier already rounded to half precision
+    float row_scale;
+    if (MODE == STATIC) {
+      if (p.scale_input) {
+        row_scale = *p.scale_input;
+        inv_h = round_half<T>(__frcp_rn(row_scale));
+      } else {
+        row_scale = 1.f;
+        inv_h = 1.f;
+      }
+    } else {
+      float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          am0 = fmax3(am0, fabsf(f[c][i]), fabsf(f[c][i + 1]));
+          am1 = fmax3(am1, fabsf(f[c][i + 2]), fabsf(f[c][i + 3]));
+        }
+      const float am = row_reduce<WPR, true>(fmaxf(am0, am1), &red[2][0][0], par, warp);
+      row_scale = (am > 0.f) ? __fdiv_rn(am, 448.f) : 1.f;
+      inv_h = round_half<T>(__frcp_rn(row_scale));
+    }
+    if (live) {
+      if (t == 0) p.qscale[row] = row_scale;
+      uint8_t* qr = p.q + row * p.K;
+      const float2 i2 = make_float2(inv_h, inv_h);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int ch = t + c * GT;
+        if (ch < nchunks) {
+          uint32_t o[4];
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            // product formed in half precision, then rounded to e4m3
+            const float2 p01 = round_half2<T>(mul2(make_float2(f[c][i], f[c][i + 1]), i2));
+            const float2 p23 = round_half2<T>(mul2(make_float2(f[c][i + 2], f[c][i + 3]), i2));
+            o[i >> 2] = cvt_e4m3x4(p01.x, p01.y, p23.x, p23.y);
+          }
+          *reinterpret_cast<uint4*>(qr + ch * CHUNK) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+}
+
 template <typename T, int MODE> int launch_t(const Params& p, cudaStream_t st) {
+  const bool wide = p.K > 8192;
   size_t smem = 0;
   if (MODE == ADALN && p.mod_rows == 1) smem = 2 * p.K * sizeof(T);
   if (MODE == LN_AFFINE) smem = 2 * p.K * sizeof(float);
   // narrow rows: 1 or 2 warps per row and 4 chunks per thread; wide rows: all 4 warps on one row
   const int wpr = p.K <= 2048 ? 1 : (p.K <= 4096 ? 2 : 4);
-  const bool wide = p.K > 8192;
   const int rpc = 4 / wpr;
   const int64_t want = (p.M + rpc - 1) / rpc;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -263,10 +473,19 @@ template <typename T, int MODE> int launch_t(const Params& p, cudaStream_t st) {
       return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");                                                     \
     rowwise_kernel<T, MODE, W, NC><<<grid, THREADS, smem, st>>>(p);                                                              \
   } while (0)
-  if (wpr == 1) KSB_RQ_LAUNCH(1, 4);
-  else if (wpr == 2) KSB_RQ_LAUNCH(2, 4);
-  else if (!wide) KSB_RQ_LAUNCH(4, 4);
-  else KSB_RQ_LAUNCH(4, 8);
+#define KSB_RQ_LAUNCH_F32(W, NC)                                                                                                  \
+  do {                                                                                                                           \
+    if (smem > 48 * 1024 &&                                                                                                      \
+        cudaFuncSetAttribute(rowwise_f32_kernel<T, MODE, W, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");                                                     \
+    rowwise_f32_kernel<T, MODE, W, NC><<<grid, THREADS, smem, st>>>(p);                                                          \
+  } while (0)
+  const bool three = p.K <= static_cast<int64_t>(wpr) * 32 * CHUNK * 3;  // three chunks per thread are enough
+  if (wide) KSB_RQ_LAUNCH(4, 8);
+  else if (wpr == 1) { if (three) KSB_RQ_LAUNCH_F32(1, 3); else KSB_RQ_LAUNCH_F32(1, 4); }
+  else if (wpr == 2) { if (three) KSB_RQ_LAUNCH_F32(2, 3); else KSB_RQ_LAUNCH_F32(2, 4); }
+  else { if (three) KSB_RQ_LAUNCH_F32(4, 3); else KSB_RQ_LAUNCH_F32(4, 4); }
+#undef KSB_RQ_LAUNCH_F32
 #undef KSB_RQ_LAUNCH
   return check_launch("rowwise quantiser");
 }

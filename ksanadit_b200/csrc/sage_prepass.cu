@@ -114,13 +114,16 @@ __global__ void __launch_bounds__(BLOCK * 4) int8_block_quant_kernel(const T* __
   for (int i = 0; i < VEC; ++i) {
     const int j = threadIdx.x + i * NT;
     const int r = j >> 4, c = (j & 15) * 8;
-    uint32_t w[2] = {0, 0};
+    // round-half-even to an integer without a conversion instruction: adding 1.5 * 2^23 leaves the two's
+    // complement integer in the low mantissa bits (|x * inv| <= 127 * (1 + 2^-23) by construction, so the
+    // clamp to +-127 can never bind); the low bytes of four sums are gathered with byte permutes
+    uint32_t t[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      int q = __float2int_rn(__fmul_rn(v[i][e], inv));
-      q = max(-127, min(127, q));
-      w[e >> 2] |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e & 3));
-    }
+    for (int e = 0; e < 8; ++e) t[e] = __float_as_uint(__fadd_rn(__fmul_rn(v[i][e], inv), 12582912.f));
+    uint32_t w[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+      w[g] = __byte_perm(__byte_perm(t[4 * g], t[4 * g + 1], 0x0040), __byte_perm(t[4 * g + 2], t[4 * g + 3], 0x0040), 0x5410);
     *reinterpret_cast<uint2*>(out + ((int64_t)h * Lpad + l0 + r) * D + c) = make_uint2(w[0], w[1]);
   }
 }
