@@ -283,24 +283,44 @@ __global__ void __launch_bounds__(NR_THREADS, 4) rmsnorm_rope_kernel(T* __restri
         if (rg.diag) ch = cw = cf;
       }
     }
+    // A thread's vectors are 1024 channels (8 heads) apart, so they all cover the same four rotation pairs of
+    // their heads: the (cos, sin) entries -- and a per-head weight -- are fetched once per row, not per vector.
+    static_assert((NR_THREADS * 8) % D == 0, "a thread's vectors must fall on the same channels of their heads");
+    const int p0 = ((threadIdx.x * 8) & (D - 1)) >> 1;
+    float2 rot[4];
+    if (ROPE && rotate) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int pr = p0 + q;
+        const int coord = pr < rg.nf ? cf : (pr < rg.nf + rg.nh ? ch : cw);
+        rot[q] = rg.table[(int64_t)coord * 64 + pr];
+      }
+    }
+    float wh[8];
+    if (PER_HEAD) {
+      const float4 w0 = *reinterpret_cast<const float4*>(w + 2 * p0), w1 = *reinterpret_cast<const float4*>(w + 2 * p0 + 4);
+      wh[0] = w0.x; wh[1] = w0.y; wh[2] = w0.z; wh[3] = w0.w; wh[4] = w1.x; wh[5] = w1.y; wh[6] = w1.z; wh[7] = w1.w;
+    }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int j = threadIdx.x + i * NR_THREADS;
       if (j < nvec) {
         const T* t = reinterpret_cast<const T*>(&cur[i]);
-        const int wofs = PER_HEAD ? ((j * 8) & (D - 1)) : j * 8;
-        const float4 w0 = *reinterpret_cast<const float4*>(w + wofs), w1 = *reinterpret_cast<const float4*>(w + wofs + 4);
-        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float wv[8];
+        if (PER_HEAD) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wv[e] = wh[e];
+        } else {
+          const float4 w0 = *reinterpret_cast<const float4*>(w + j * 8), w1 = *reinterpret_cast<const float4*>(w + j * 8 + 4);
+          wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+        }
         float y[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) y[e] = HalfOps<T>::to_f(HalfOps<T>::from_f(HalfOps<T>::to_f(t[e]) * rstd_v[i] * wv[e]));
         if (ROPE && rotate) {
-          const int p0 = ((j * 8) & (D - 1)) >> 1;  // first rotation pair of this vector inside its head
 #pragma unroll
           for (int e = 0; e < 8; e += 2) {
-            const int pr = p0 + (e >> 1);
-            const int coord = pr < rg.nf ? cf : (pr < rg.nf + rg.nh ? ch : cw);
-            const float2 cssn = rg.table[(int64_t)coord * 64 + pr];
+            const float2 cssn = rot[e >> 1];
             const float a = y[e], b = y[e + 1];
             y[e] = a * cssn.x - b * cssn.y;
             y[e + 1] = a * cssn.y + b * cssn.x;
