@@ -11,6 +11,9 @@ synchronises, so a whole step can be captured once and replayed with one launch.
 Constraints (checked where they can be): fixed shapes and dtypes; tensors only; the callable must be pure device
 work (no ``.item()``, no host-side tables built per call -- the RoPE tables are cached per shape for this reason).
 The outputs are views of graph-owned memory and are overwritten by the next replay.
+
+Single-process steps only: a step that contains collectives (a process group is initialised with more than one
+rank) is refused -- a capture with NCCL all-to-alls inside did not complete when it was tried on two GPUs.
 """
 
 from __future__ import annotations
@@ -24,6 +27,9 @@ class StepGraph:
     def __init__(self, fn, example_inputs, warmup: int = 2):
         if not all(torch.is_tensor(t) and t.is_cuda for t in example_inputs):
             raise _lib.KsanaB200Error("StepGraph needs CUDA tensors as inputs")
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            raise _lib.KsanaB200Error("StepGraph captures single-process steps only (no collectives inside a graph)")
         if ops.STATS.timing:
             raise _lib.KsanaB200Error("switch per-call event timing off before capturing (events cannot be recorded into a graph)")
         self._fn = fn

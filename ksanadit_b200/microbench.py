@@ -146,13 +146,17 @@ def run_qwen(a):
 
     L = Li_all + Lt
     if world > 1:
-        t = timeit(step, a.iters, a.warmup)
-        tt = torch.tensor([t], device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
-        if rank == 0:
-            print(f"qwen-image step on {world} GPUs (Ulysses, NCCL): {layers} blocks, {Li_all}+{Lt} tokens, {Li} image rows per rank: "
-                  f"{tt.item():.2f} ms  {fl / tt.item() / 1e9:.1f} TFLOP/s")
+
+        def report(tag, t):
+            tt = torch.tensor([t], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                print(f"qwen-image step on {world} GPUs (Ulysses, NCCL), {tag}: {layers} blocks, {Li_all}+{Lt} tokens, {Li} image rows per rank: "
+                      f"{tt.item():.2f} ms  {fl / tt.item() / 1e9:.1f} TFLOP/s", flush=True)
+
+        report("eager launches", timeit(step, a.iters, a.warmup))
+        dist.barrier()
         dist.destroy_process_group()
         return
     fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
