@@ -60,3 +60,19 @@ def test_step_graph_rejects_other_shapes():
     graph = StepGraph(lambda t: ops.quant_fp8_rowwise(t)[0], (x,))
     with pytest.raises(_lib.KsanaB200Error):
         graph(x[:32])
+
+
+def test_torch_library_ops_match_the_direct_calls():
+    import ksanadit_b200.torch_ops  # noqa: F401
+    from ksanadit_b200 import ops
+    from ksanadit_b200.linear import B200Fp8Linear, quantize_weight_per_channel
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(3, 50, 256, generator=g).to(torch.bfloat16).cuda()
+    lin = B200Fp8Linear(256, 128, device="cuda", dtype=torch.bfloat16)
+    wq, s = quantize_weight_per_channel((torch.randn(128, 256, generator=g) * 0.02).cuda())
+    lin.weight = torch.nn.Parameter(wq, requires_grad=False)
+    lin.scale_weight = torch.nn.Parameter(s, requires_grad=False)
+    lin.bias = torch.nn.Parameter((torch.randn(128, generator=g) * 0.1).to(torch.bfloat16).cuda(), requires_grad=False)
+    assert torch.equal(torch.ops.ksana_b200.fp8_linear(x, lin.weight, lin.scale_weight, lin.bias), lin(x))
+    q, k, v = (torch.randn(200, 2, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    assert torch.equal(torch.ops.ksana_b200.sage_attention(q, k, v), ops.sage_attention(q, k, v))

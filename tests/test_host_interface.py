@@ -201,3 +201,24 @@ print("install ok")
 """
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "install ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_torch_library_ops_have_shape_inference():
+    """The registered operators can be traced with fake tensors (no kernel runs) and refuse CPU tensors."""
+    import pytest
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    import ksanadit_b200.torch_ops  # noqa: F401  (registers torch.ops.ksana_b200.*)
+    with FakeTensorMode():
+        x = torch.empty(2, 7, 64, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(48, 64, dtype=torch.float8_e4m3fn, device="cuda")
+        s = torch.empty(48, dtype=torch.float32, device="cuda")
+        y = torch.ops.ksana_b200.fp8_linear(x, w, s, None)
+        assert y.shape == (2, 7, 48) and y.dtype == torch.bfloat16
+        q = torch.empty(100, 4, 128, dtype=torch.float16, device="cuda")
+        o = torch.ops.ksana_b200.sage_attention(q, q, q)
+        assert o.shape == q.shape and o.dtype == torch.float16
+    with pytest.raises(Exception):
+        torch.ops.ksana_b200.sage_attention(torch.zeros(8, 1, 128, dtype=torch.bfloat16), torch.zeros(8, 1, 128, dtype=torch.bfloat16),
+                                            torch.zeros(8, 1, 128, dtype=torch.bfloat16))
