@@ -61,9 +61,9 @@ def gather_heads(x: torch.Tensor, group=None) -> torch.Tensor:
     if P == 1:
         return x
     L, Hl, D = x.shape
-    buf = torch.empty(P, L, Hl, D, dtype=x.dtype, device=x.device)
+    buf = torch.empty(P * L, Hl, D, dtype=x.dtype, device=x.device)  # rank-major concatenation
     dist.all_gather_into_tensor(buf, x.contiguous(), group=group)
-    return buf.permute(1, 0, 2, 3).reshape(L, P * Hl, D)
+    return buf.view(P, L, Hl, D).permute(1, 0, 2, 3).reshape(L, P * Hl, D)
 
 
 def sequence_to_heads(x: torch.Tensor, group=None) -> torch.Tensor:

@@ -154,6 +154,13 @@ assert torch.equal(h2s, exp), "heads_to_sequence"
 s2h = distribute.sequence_to_heads(h2s[:, 0].contiguous())
 assert torch.equal(s2h, qkv[r][:, 0]), "sequence_to_heads"
 assert torch.equal(distribute.gather_forward(full[r], dim=1), torch.cat(full, dim=1))
+# receive straight into the tail of a joint [text; image] buffer (Qwen block) and gather replicated text heads
+joint = torch.zeros(2 + P * 6, 3, 4 // P, 8)
+distribute.heads_to_sequence(qkv[r].clone(), out=joint[2:])
+assert torch.equal(joint[2:], exp) and bool((joint[:2] == 0).all()), "heads_to_sequence(out=)"
+txt = torch.randn(5, 4, 8, generator=g)                                   # replicated on every rank
+got_txt = distribute.gather_heads(txt[:, r * (4 // P):(r + 1) * (4 // P)].contiguous())
+assert torch.equal(got_txt, txt), "gather_heads"
 dist.barrier(); dist.destroy_process_group()
 print("rank", r, "ok")
 """
