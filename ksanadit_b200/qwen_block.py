@@ -46,6 +46,7 @@ class B200QwenBlock(torch.nn.Module):
             m = torch.nn.Module()
             m.weight = torch.nn.Parameter(torch.ones(HEAD, device=device, dtype=torch.float32), requires_grad=False)
             setattr(self.attn, n, m)
+        self._mod_fused = None  # (key, weight [12 dim, dim] e4m3, scales, bias) of img_mod | txt_mod, built on first use
         for s in ("img_mlp", "txt_mlp"):
             mlp = torch.nn.Module()
             act = torch.nn.Module()
@@ -106,6 +107,24 @@ class B200QwenBlock(torch.nn.Module):
         return self
 
     # ------------------------------------------------------------------ forward
+    def _modulation(self, st):
+        """img_mod and txt_mod (transformer.py:204-211) as ONE GEMM: both are Linears of the same one-row input, and at
+        one row a GEMM only streams its weight, so two launches cost twice the fixed part.  The two weights are
+        concatenated once; the modules' own parameters become views of the concatenation (no second copy)."""
+        im, tm = self.img_mod[1], self.txt_mod[1]
+        key = (im.weight.data_ptr(), tm.weight.data_ptr(), im.scale_weight.data_ptr(), tm.scale_weight.data_ptr())
+        if self._mod_fused is None or self._mod_fused[0] != key:
+            w = torch.cat([im.weight.data, tm.weight.data], dim=0).contiguous()
+            sc = torch.cat([im.weight_scale_vector(), tm.weight_scale_vector()]).contiguous()
+            b = torch.cat([im.bias.data, tm.bias.data]).contiguous() if im.bias is not None else None
+            n = im.out_features
+            im.weight.data, tm.weight.data = w[:n], w[n:]
+            key = (im.weight.data_ptr(), tm.weight.data_ptr(), im.scale_weight.data_ptr(), tm.scale_weight.data_ptr())
+            self._mod_fused = (key, w, sc, b)
+        _, w, sc, b = self._mod_fused
+        xq, sx = ops.quant_fp8_rowwise(st)
+        return ops.fp8_gemm(xq, sx, w, sc, b, out_dtype=self.dtype)
+
     def _stream_tail(self, x, attn_out, gate1, mod2, out_lin, mlp):
         """x + gate1 * out(attn_out), then x + gate2 * mlp(modulate(LN(x)))  (transformer.py:225-234)."""
         aq, sa = ops.quant_fp8_rowwise(attn_out)
@@ -136,8 +155,9 @@ class B200QwenBlock(torch.nn.Module):
         Hl = H // P
         img_tab, txt_tab = ops.qwen_rope_tables(img_grid, Lt, device=img.device)
         st = torch.nn.functional.silu(temb)
-        imod = self.img_mod[1](st)[0].view(2, 3, 1, C)  # [mod1|mod2] x [shift|scale|gate]
-        tmod = self.txt_mod[1](st)[0].view(2, 3, 1, C)
+        mods = self._modulation(st)  # [1, 12 C]: image then text, each [mod1|mod2] x [shift|scale|gate]
+        imod = mods[0, :6 * C].view(2, 3, 1, C)
+        tmod = mods[0, 6 * C:].view(2, 3, 1, C)
 
         # local projections: text rows first (attention.py:355-357), then this rank's image rows
         qkv = torch.empty(Lt + Li, 3 * C, dtype=self.dtype, device=img.device)
