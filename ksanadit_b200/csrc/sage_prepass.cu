@@ -70,7 +70,7 @@ __global__ void mean_finish_kernel(const float* __restrict__ partial, int chunks
 // grid (Lpad / BLOCK, H).  A block of BLOCK tokens x 128 channels lives in registers between the
 // absmax reduction and the quantisation.
 template <typename T, int BLOCK>
-__global__ void __launch_bounds__(BLOCK * 4) int8_block_quant_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs,
+__global__ void __launch_bounds__(BLOCK * 4, BLOCK == 128 ? 3 : 6) int8_block_quant_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs,
                                                                     float premul, const float* __restrict__ mean,
                                                                     int8_t* __restrict__ out, float* __restrict__ scale,
                                                                     int64_t Lpad) {
@@ -79,26 +79,39 @@ __global__ void __launch_bounds__(BLOCK * 4) int8_block_quant_kernel(const T* __
   __shared__ float red[NT / 32];
   const int h = blockIdx.y, b = blockIdx.x;
   const int64_t l0 = (int64_t)b * BLOCK;
-  float v[VEC][8];
+  // The block stays in registers in its packed form (16 registers, not 32 of fp32) and is unpacked in both
+  // passes: the lower register count lets a third (sixth) CTA share the SM, which hides the load latency of
+  // these single-shot CTAs better than saving the second unpack would.
+  uint4 raw[VEC];
+  const int c = (threadIdx.x & 15) * 8;     // NT is a multiple of 16: the same 8 channels in every vector of a thread
+  float mu[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) mu[e] = mean ? mean[h * D + c + e] : 0.f;
+  auto value = [&](const uint4& r, float (&f)[8]) {
+    const T* t = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float v = HalfOps<T>::to_f(t[e]);
+      if (mean) v = v - mu[e];
+      if (premul != 0.f) v = v * premul;
+      f[e] = v;
+    }
+  };
   float am = 0.f;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int j = threadIdx.x + i * NT;
-    const int r = j >> 4, c = (j & 15) * 8;
-    const int64_t l = l0 + r;
-    if (l < L) {
-      load8<T>(x + l * ts + (int64_t)h * hs + c, v[i]);
+    const int64_t l = l0 + (j >> 4);
+    raw[i] = (l < L) ? *reinterpret_cast<const uint4*>(x + l * ts + (int64_t)h * hs + c) : make_uint4(0, 0, 0, 0);
+  }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float f = v[i][e];
-        if (mean) f = f - mean[h * D + c + e];
-        if (premul != 0.f) f = f * premul;
-        v[i][e] = f;
-        am = fmaxf(am, fabsf(f));
-      }
-    } else {
+  for (int i = 0; i < VEC; ++i) {
+    const int j = threadIdx.x + i * NT;
+    if (l0 + (j >> 4) < L) {
+      float f[8];
+      value(raw[i], f);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+      for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(f[e]));
     }
   }
   am = warp_max(am);
@@ -113,13 +126,20 @@ __global__ void __launch_bounds__(BLOCK * 4) int8_block_quant_kernel(const T* __
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int j = threadIdx.x + i * NT;
-    const int r = j >> 4, c = (j & 15) * 8;
+    const int r = j >> 4;
+    float f[8];
+    if (l0 + r < L) {
+      value(raw[i], f);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;  // padding rows quantise to 0 whatever the mean
+    }
     // round-half-even to an integer without a conversion instruction: adding 1.5 * 2^23 leaves the two's
     // complement integer in the low mantissa bits (|x * inv| <= 127 * (1 + 2^-23) by construction, so the
     // clamp to +-127 can never bind); the low bytes of four sums are gathered with byte permutes
     uint32_t t[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) t[e] = __float_as_uint(__fadd_rn(__fmul_rn(v[i][e], inv), 12582912.f));
+    for (int e = 0; e < 8; ++e) t[e] = __float_as_uint(__fadd_rn(__fmul_rn(f[e], inv), 12582912.f));
     uint32_t w[2];
 #pragma unroll
     for (int g = 0; g < 2; ++g)
