@@ -237,7 +237,7 @@ __global__ void rstd_scatter_kernel(const float* __restrict__ tile_sumsq, int ti
 }
 
 template <typename T, bool ROPE, bool PER_HEAD, int NV>
-__global__ void __launch_bounds__(NR_THREADS, 4) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
+__global__ void __launch_bounds__(NR_THREADS, NV <= 5 ? 6 : 4) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
                                                                      const float* __restrict__ w, float eps, RopeGrid rg,
                                                                      const float* __restrict__ row_rstd) {
   __shared__ float red[2][NR_THREADS / 32];
@@ -462,7 +462,8 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
   const int blocks = (int)(L < cap ? L : cap);
   const bool wide = C > prep::NR_THREADS * 8 * 4;  // more than 4 vectors per thread
 #define KSB_LAUNCH_NR(T, R, P, NV) prep::rmsnorm_rope_kernel<T, R, P, NV><<<blocks, prep::NR_THREADS, 0, st>>>(static_cast<T*>(x), L, (int)C, ld, w, eps, rg, row_rstd)
-#define KSB_LAUNCH_NR3(T, R, P) do { if (wide) KSB_LAUNCH_NR(T, R, P, 8); else KSB_LAUNCH_NR(T, R, P, 4); } while (0)
+  const bool five = C > prep::NR_THREADS * 8 * 4 && C <= prep::NR_THREADS * 8 * 5;  // e.g. 5120: five vectors per thread, six CTAs per SM
+#define KSB_LAUNCH_NR3(T, R, P) do { if (five) KSB_LAUNCH_NR(T, R, P, 5); else if (wide) KSB_LAUNCH_NR(T, R, P, 8); else KSB_LAUNCH_NR(T, R, P, 4); } while (0)
 #define KSB_LAUNCH_NR2(T)                                                          \
   do {                                                                             \
     if (rope_table) { if (per_head) KSB_LAUNCH_NR3(T, true, true); else KSB_LAUNCH_NR3(T, true, false); } \
