@@ -154,22 +154,39 @@ class B200RadialSageAttentionImpl(KsanaAttentionBackendImpl):
         _, _, num_frame, l_h, l_w = latent_shape
         if l_h % (self.block_size // 8) != 0 or l_w % (self.block_size // 8) != 0:
             raise ValueError(f"output's width and height must be divisible by block size {self.block_size}")
+        # The reference builds the mask for query.shape[1] tokens and hands the whole sequence to its kernel (its
+        # `[:, :, :video_token_num]` slice acts on the head axis of an NHD tensor, radial_sage_attn.py:170-176):
+        # the lists below cover exactly the length the kernel gets, and the output keeps the input's shape.
+        if key.shape[1] != query.shape[1]:
+            raise ValueError("radial attention is self-attention: key and query lengths must match")
         lists = self.tile_lists_for(query.shape[1], video_tokens, int(num_frame), query.device)
-        q, k, v = (t[:, :video_tokens] for t in (query, key, value))  # the reference slices dim 2 here (:171-173), a no-op in NHD
-        return _run_sage(q, k, v, lists)
+        return _run_sage(query, key, value, lists)
 
     def tile_lists_for(self, seq_len, video_tokens, num_frame, device):
+        """(offsets [nq + 1], entries, order [nq]) device tensors for a sequence of ``seq_len`` tokens, nq = ceil(seq_len / 128).
+
+        ``MaskMap`` yields seq_len // block_size rows; a ragged last block (seq_len not a multiple of 128, e.g. 21
+        frames of 64 tokens) is kept dense in both directions, like every row and column past the video tokens."""
         key = (seq_len, self.block_size, self.decay_factor, video_tokens, num_frame, str(device))
         cache = B200RadialSageAttentionImpl._global_cache
         if key not in cache:
-            m = radial_mask.build_radial_tile_mask(seq_len, video_tokens, num_frame, self.block_size, self.decay_factor)
-            m = radial_mask.expand_to_kernel_granularity(m, self.block_size)
+            bs = self.block_size
+            if bs not in (64, 128):
+                raise ValueError(f"block_size must be 64 or 128, got {bs}")
+            m = radial_mask.build_radial_tile_mask(seq_len, video_tokens, num_frame, bs, self.decay_factor)
+            nq = (seq_len + 127) // 128
+            full = np.ones((nq * (128 // bs), nq * (128 // bs)), dtype=bool)
+            full[: m.shape[0], : m.shape[1]] = m
+            m = radial_mask.expand_to_kernel_granularity(full, bs)
             offs, ents = radial_mask.compact_tile_lists(m)
+            order = radial_mask.longest_first_order(offs)
+            # what the kernel indexes with: nq + 1 offsets, nq order entries, KV tile numbers below ceil(seq_len / 128)
+            if offs.size != nq + 1 or order.size != nq or (ents.size and int((ents >> 2).max()) >= nq) or int(offs[-1]) != ents.size:
+                raise _lib.KsanaB200Error("radial tile lists do not match the kernel's block counts")
             if ents.size == 0:
                 ents = np.zeros(1, dtype=np.int32)  # keep a valid pointer for an all-empty mask
             if len(cache) >= self._max_cache_size:
                 cache.popitem(last=False)
-            order = radial_mask.longest_first_order(offs)
             cache[key] = (torch.from_numpy(offs).to(device), torch.from_numpy(ents).to(device), torch.from_numpy(order).to(device))
         return cache[key]
 

@@ -3,24 +3,34 @@
 //   S = Q8 . K8^T            tcgen05.mma kind::i8   (s32 accumulator in tensor memory, see below)
 //   X = float(S) * qs * ks   fp32, exp2 domain (softmax scale and log2 e are folded into Q8's scale)
 //   P = exp2(X - m + 8)      fp32 online softmax against the exact running row maximum, rounded to e4m3
-//   O += P . V8              tcgen05.mma kind::f8f6f4 (f32 accumulator in tensor memory)
+//   O += P . V8              tcgen05.mma kind::f8f6f4, P read from tensor memory (f32 accumulator in tensor memory)
 //   out = O / l * vs
 //
 // One CTA works on one (head, 128-row Q block) at a time and walks that block's list of 128-token KV
-// tiles; two CTAs share an SM (256 tensor-memory columns and ~98 KB of shared memory each), so one
+// tiles; two CTAs share an SM (256 tensor-memory columns and ~82 KB of shared memory each), so one
 // CTA's softmax overlaps the other's MMAs.  Warp roles inside a CTA:
 //   warp 0      TMA producer (Q block once per work item; K and V^T tiles through 2-deep rings)
-//   warp 1      MMA issuer (single thread): S = Q.K^T for tile j+1 is queued before P.V of tile j; P alternates between two shared-memory buffers
+//   warp 1      MMA issuer (single thread): S_0, then per tile  O += P_j . V_j  followed by  S_{j+1} = Q . K_{j+1}^T
 //   warps 2,3   idle (they only donate registers)
-//   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written to shared memory
-//               in the 128-byte-swizzled K-major layout the MMA reads, O rescaled in tensor memory in the
-//               tiles where a row maximum of the warp grew; final normalisation and store
-// The s32 score accumulator is pre-loaded with 0x4B400000 before every S = Q.K^T (tcgen05.cp copies of a constant
-// shared-memory block, queued by the MMA issuer in front of the MMAs) and the MMA accumulates on top of it: the bit pattern read back, taken as an fp32, is exactly 12582912 + S (|S| < 2^22), so the
-// scores need no integer-to-float conversion and X = fma(bits_as_float, scale, -12582912 * scale - m + 8).
+//   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written back with tcgen05.st over
+//               the first 32 columns of S (four scores per 32-bit column, the layout the MMA reads its A operand
+//               in), O rescaled in tensor memory in the tiles where a row maximum of the warp grew; final
+//               normalisation and store
+// P never touches shared memory: a 128 x 128 tile then reads Q, K (S = Q.K^T) and V (P.V) from shared memory and
+// nothing else, 48 KB per tile instead of the 128 KB of a shared-memory P and a copied accumulator pre-load --
+// shared-memory read bandwidth (128 B / clk), not the tensor pipe, bounded the earlier form of this kernel.
+// Because P overwrites S, S_{j+1} is issued after P_j . V_j; the barrier that announces S_{j+1} therefore also
+// says that O holds every product up to tile j, which is what the O rescale needs.
+//
+// The s32 score accumulator must read back as an fp32 number: every S = Q.K^T starts with one bf16 MMA
+// (A = 1 at k = 0 and 8, B = 1.5 * 2^22 at k = 0 and 8, both from constant shared-memory blocks) that writes
+// 12582912.0f = 0x4B400000 to all 128 x 128 accumulators, and the INT8 MMAs accumulate on top of those bits: taken as
+// fp32 they are exactly 12582912 + S (|S| < 2^22), so the scores need no integer-to-float conversion and
+// X = fma(bits_as_float, scale, -12582912 * scale - m + 8).
 // Every mbarrier wait is bounded (see common.cuh).
 //
-// Tensor-bound: 4 * 128 * 128 * 128 flop per visited (Q block, KV tile) pair.
+// Tensor-bound: 4 * 128 * 128 * 128 flop per visited (Q block, KV tile) pair; the 16 384 exp2 of a tile cost
+// 1024 cycles of the special-function unit against 512 tensor-pipe cycles, which is the practical ceiling.
 #include "../../include/ksana_b200.h"
 #include "common.cuh"
 #include "host_utils.h"
@@ -33,17 +43,15 @@ constexpr int UMMA_K = 32;
 constexpr int KST = 2, VST = 2;
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int THREADS = 256;
-constexpr int TMEM_COLS = 256;  // S: columns 0..127 (s32), O: columns 128..255 (f32)
+constexpr int TMEM_COLS = 256;  // S: columns 0..127 (s32; P as packed e4m3 over columns 0..31), O: columns 128..255 (f32)
 constexpr int KERNEL_ID = 2;
-constexpr uint32_t S_MAGIC_BITS = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23: one ulp is 1 on [2^23, 2^24)
-constexpr float S_MAGIC = 12582912.0f;
+constexpr float S_MAGIC = 12582912.0f;  // 1.5 * 2^23 = 0x4B400000: one ulp is 1 on [2^23, 2^24)
 constexpr float P_SHIFT = 8.0f;  // P carries a static factor 2^8 into e4m3: the row maximum maps to 256 exactly
-constexpr int PST = 2;  // P buffers: P of tile g goes to buffer g & 1, so it never waits for the previous P.V
-constexpr int NUM_BARS = 16;
-// Q | P x PST | K x KST | V x VST | barriers.  The dynamic shared memory window itself must be 1024-byte aligned
+constexpr int NUM_BARS = 18;
+// Q | K x KST | V x VST | constants | barriers.  The dynamic shared memory window itself must be 1024-byte aligned
 // (checked at kernel start): with two CTAs per SM there is no room for alignment slack.
-constexpr int NUM_TILES = 1 + PST + KST + VST;
-constexpr int CONST_BYTES = 512;  // S_MAGIC_BITS words the score-accumulator pre-load copies from
+constexpr int NUM_TILES = 1 + KST + VST;
+constexpr int CONST_BYTES = 1024;  // two 512-byte blocks of repeated 16-byte chunks: A and B of the accumulator pre-load MMA
 constexpr int SMEM_BYTES = NUM_TILES * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS + 64;
 
 struct Params {
@@ -101,38 +109,6 @@ __device__ __forceinline__ float tree_max64(const uint32_t (&a)[32], const uint3
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-#ifndef KSB_ATTN_POLY
-#define KSB_ATTN_POLY 0  // share of the exponentials evaluated on the FMA pipe: 0 = none, 1 = 1/4, 2 = 1/2
-#endif
-#ifdef KSB_ATTN_TIMING
-// development instrumentation: cycles spent by softmax warp 4 of every CTA in each phase of the tile loop
-__device__ unsigned long long g_attn_phase_cycles[16];
-#define KSB_T(i)                                                   \
-  do {                                                             \
-    const long long now_ = clock64();                              \
-    ph_[i] += now_ - tprev_;                                       \
-    tprev_ = now_;                                                 \
-  } while (0)
-#else
-#define KSB_T(i)
-#endif
-
-// 2^x for two values on the FMA / ALU pipes instead of the special-function unit: x = n + r with n the
-// nearest integer (taken from the low mantissa bits of x + 1.5 * 2^23) and r in [-0.5, 0.5]; 2^r by a
-// cubic (relative error < 8e-5, far below the e4m3 rounding step), n added to the exponent field.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
-  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-  const float2 r = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-  float2 q = __ffma2_rn(r, make_float2(0.05508868396282196f, 0.05508868396282196f), make_float2(0.24260404706001282f, 0.24260404706001282f));
-  q = __ffma2_rn(q, r, make_float2(0.6932762265205383f, 0.6932762265205383f));
-  q = __ffma2_rn(q, r, make_float2(0.9999289512634277f, 0.9999289512634277f));
-  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23)));
-}
-
 // P = exp2(f * sc + c) for one 32-score chunk (f = 12582912 + S as fp32) -> 8 words of packed e4m3; the
 // exact (unrounded) values are added into four independent packed accumulators.  A masked score holds -inf
 // and yields 0 (or 2^-126, which rounds to 0 and vanishes in the row sum).
@@ -143,8 +119,7 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], float sc, flo
     const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc2, c2);
     const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc2, c2);
     const float2 e01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
-    const bool poly = (KSB_ATTN_POLY == 2) || (KSB_ATTN_POLY == 1 && ((i >> 2) & 1));
-    const float2 e23 = poly ? exp2_poly2(x23) : make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+    const float2 e23 = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
     acc[(i >> 2) & 3] = __fadd2_rn(acc[(i >> 2) & 3], e01);
     acc[((i >> 2) + 2) & 3] = __fadd2_rn(acc[((i >> 2) + 2) & 3], e23);
     pk[i >> 2] = cvt_e4m3x4(e01.x, e01.y, e23.x, e23.y);
@@ -158,15 +133,15 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* gen = smem_raw;
-  const uint32_t q_smem = base, p_smem = base + TILE_BYTES;
-  const uint32_t k_smem = base + (1 + PST) * TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = base + TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
   const uint32_t const_smem = v_smem + VST * TILE_BYTES;
   const uint32_t bars = const_smem + CONST_BYTES;
-  const uint32_t q_full = bars, q_empty = bars + 8, k_full = bars + 16, k_empty = bars + 32, v_full = bars + 48,
-                 v_empty = bars + 64, s_full = bars + 80, s_empty = bars + 88, p_full = bars + 96, p_empty = bars + 112;  // p_*: PST each
+  const uint32_t q_full = bars, q_empty = bars + 8, k_full = bars + 16, k_empty = bars + 16 + 8 * KST, v_full = bars + 16 + 16 * KST,
+                 v_empty = v_full + 8 * VST, s_full = v_empty + 8 * VST, p_full = s_full + 8, o_full = s_full + 16;
+  static_assert(2 + 2 * KST + 2 * VST + 3 <= NUM_BARS, "barrier block too small");
   const uint32_t tmem_slot = bars + 8 * NUM_BARS + 16;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + NUM_TILES * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS + 16);
-  uint8_t* p_gen = gen + TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total = p.H * p.nq;
@@ -181,13 +156,16 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int s = 0; s < KST; ++s) { mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1); }
     for (int s = 0; s < VST; ++s) { mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1); }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
-    for (int b = 0; b < PST; ++b) { mbar_init(p_full + 8 * b, 4); mbar_init(p_empty + 8 * b, 1); }
+    mbar_init(p_full, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
+    mbar_init(o_full, 1);
     fence_barrier_init();
   }
   if (threadIdx.x < CONST_BYTES / 4) {
-    reinterpret_cast<uint32_t*>(gen + NUM_TILES * TILE_BYTES)[threadIdx.x] = S_MAGIC_BITS;
-    fence_proxy_async_smem();  // read by the tensor-memory copy engine
+    // bf16 operands of the pre-load MMA, every 16-byte chunk (8 values along k) the same within a block:
+    // A chunk = {1, 0, ...}, B chunk = {1.5 * 2^22, 0, ...}; a row's k = 0..15 are two such chunks
+    const uint32_t word = (threadIdx.x & 3) ? 0u : (threadIdx.x < CONST_BYTES / 8 ? 0x3F80u : 0x4AC0u);
+    reinterpret_cast<uint32_t*>(gen + NUM_TILES * TILE_BYTES)[threadIdx.x] = word;
+    fence_proxy_async_smem();  // read by the tensor core
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -237,22 +215,22 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = IDESC_S8_S32(BQ, BKV);
       constexpr uint32_t idesc_pv = IDESC_F8_E4M3_F32(BQ, D);
+      constexpr uint32_t idesc_pre = IDESC_BF16_F32(BQ, BKV);
       const uint64_t dq = make_kmajor_sw128_desc(q_smem);
-      // constant block: every word is the same, so only the footprint of the descriptor matters -- two core
-      // matrices 128 B apart along a row, sixteen row groups 16 B apart, all inside the 512-byte block
-      const uint64_t dconst = make_noswizzle_desc(const_smem, 128, 16);
+      // constant blocks: every 16-byte chunk of a block is the same, so only the footprint of the descriptors
+      // matters -- core matrices 16 B apart in both directions stay inside the 512-byte block
+      const uint64_t dca = make_noswizzle_desc(const_smem, 16, 16);
+      const uint64_t dcb = make_noswizzle_desc(const_smem + CONST_BYTES / 2, 16, 16);
       uint32_t wi = 0, itk = 0, itv = 0, g = 0;
       bool ok = true;
-      auto issue_qk = [&](uint32_t gg) -> bool {
+      // S = 12582912 + Q.K^T for the next K tile of the ring; the caller guarantees that the softmax warps are done
+      // with the previous S and that every MMA reading the previous P has been issued
+      auto issue_qk = [&]() -> bool {
         const uint32_t s = itk % KST, ph = (itk / KST) & 1;
         if (!mbar_wait(k_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 4)) return false;
-        if (!mbar_wait(s_empty, gg & 1, p.status, (KERNEL_ID << 16) | 5)) return false;  // S read by the softmax warps (completion #gg)
         tc_fence_after();
         const uint64_t dk = make_kmajor_sw128_desc(k_smem + s * TILE_BYTES);
-        // pre-load the accumulator: 16 copies of 128 rows x 32 B, executed in order in front of the MMAs
-#pragma unroll
-        for (int c = 0; c < BKV; c += 8)
-          asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_s + c), "l"(dconst) : "memory");
+        mma_bf16_ss(tmem_s, dca, dcb, idesc_pre, 0);
 #pragma unroll
         for (int kk = 0; kk < D / UMMA_K; ++kk) mma_i8_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_qk, 1);  // on top of the pre-load
         mma_commit(s_full);
@@ -264,26 +242,25 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const Work w = get_work(p, idx);
         if (w.n == 0) continue;
         if (!mbar_wait(q_full, wi & 1, p.status, (KERNEL_ID << 16) | 6)) { ok = false; break; }
-        if (!issue_qk(g)) { ok = false; break; }
+        if (!issue_qk()) { ok = false; break; }
+        if (w.n == 1) mma_commit(q_empty);  // the work item's last S = Q.K^T has been issued: Q may be replaced once it completes
         for (int j = 0; j < w.n; ++j) {
-          if (j + 1 < w.n) {
-            if (!issue_qk(g + 1)) { ok = false; break; }
-          } else {
-            mma_commit(q_empty);  // every S = Q.K^T of this work item has been issued
-          }
           const uint32_t s = itv % VST, ph = (itv / VST) & 1;
           if (!mbar_wait(v_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 7)) { ok = false; break; }
-          const uint32_t pb = g & 1, pph = (g >> 1) & 1;
-          if (!mbar_wait(p_full + 8 * pb, pph, p.status, (KERNEL_ID << 16) | 8)) { ok = false; break; }
-          const uint64_t dp = make_kmajor_sw128_desc(p_smem + pb * TILE_BYTES);
+          if (!mbar_wait(p_full, g & 1, p.status, (KERNEL_ID << 16) | 8)) { ok = false; break; }
           tc_fence_after();
           const uint64_t dv = make_kmajor_sw128_desc(v_smem + s * TILE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BKV / UMMA_K; ++kk) mma_f8_ss(tmem_o, dp + 2 * kk, dv + 2 * kk, idesc_pv, (j | kk) != 0);
-          mma_commit(p_empty + 8 * pb);
+          for (int kk = 0; kk < BKV / UMMA_K; ++kk) mma_f8_ts(tmem_o, tmem_s + 8 * kk, dv + 2 * kk, idesc_pv, (j | kk) != 0);
           mma_commit(v_empty + 8 * s);
           ++itv;
           ++g;
+          if (j + 1 < w.n) {
+            if (!issue_qk()) { ok = false; break; }
+            if (j + 2 == w.n) mma_commit(q_empty);
+          } else {
+            mma_commit(o_full);  // every P.V of this work item has completed: O is final
+          }
         }
         ++wi;
       }
@@ -296,16 +273,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t lane_sel = static_cast<uint32_t>(qrt * 32) << 16;
     const int nk64 = p.nkv * 2;
     T* out = static_cast<T*>(p.out);
-    uint32_t g = 0;
+    uint32_t g = 0, wi = 0;
     bool ok = true;
-#ifdef KSB_ATTN_TIMING
-    long long ph_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    long long tprev_ = clock64();
-#endif
-    // the score accumulator is free for the first S = Q.K^T (completion #0 of s_empty)
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(s_empty);
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
       const Work w = get_work(p, idx);
       const int qrow = w.qt * BQ + row;
@@ -325,7 +294,6 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       const float qsc = p.qs[w.h * p.nq + w.qt];
       float m_used = -INFINITY, l = 0.f;
-      KSB_T(9);
       // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
       int e_next = entry_at(w, 0);
       float ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)], ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
@@ -340,22 +308,15 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int t = e >> 2, halves = e & 3;
         const int valid = min(BKV, p.Lk - t * BKV);
         const bool full = (halves == 3) && (valid == BKV);
-        KSB_T(0);
+        // S_j is complete, and so is every P.V up to tile j - 1 (issued before it)
         if (!mbar_wait_warp(s_full, g & 1, p.status, (KERNEL_ID << 16) | 9)) { ok = false; break; }
         tc_fence_after();
-        KSB_T(1);
         uint32_t s[4][32];
         tmem_ld32(tmem_s + lane_sel + 0, s[0]);
         tmem_ld32(tmem_s + lane_sel + 32, s[1]);
         tmem_ld32(tmem_s + lane_sel + 64, s[2]);
         tmem_ld32(tmem_s + lane_sel + 96, s[3]);
         tmem_wait_ld();
-        KSB_T(2);
-        // the scores are in registers: hand the accumulator back to the MMA issuer
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_empty);
-        KSB_T(3);
         if (!full) {
           // masked columns (ragged tail or dropped 64-token half) become -inf: never the maximum, P = 0
 #pragma unroll
@@ -380,34 +341,21 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           l *= alpha;
           m_used = m_new;
         }
-        KSB_T(4);
-        // P = exp2(X - m_used + 8) -> e4m3, packed 4 per word; masked columns give exactly 0
+        // P = exp2(X - m_used + 8) -> e4m3, packed 4 per word; masked columns give exactly 0.  Each 32-score chunk
+        // goes back to tensor memory as soon as it is packed: 8 columns of this warp's own lanes, over scores the
+        // warp already holds in registers.
         const float neg_m = (m_used == -INFINITY) ? 0.f : (P_SHIFT - m_used);
-        uint32_t pk[32];
         float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         const float c0 = fmaf(-S_MAGIC, sc0, neg_m), c1 = fmaf(-S_MAGIC, sc1, neg_m);
-        // this tile's P buffer was last read by the P.V of two tiles ago; each 32-score chunk is stored as soon
-        // as it is packed (row `row` of the K-major tile: 16-byte chunks, chunk index XORed with (row & 7))
-        const uint32_t pb = g & 1, pk_use = g >> 1;
-        if (!mbar_wait_warp(p_empty + 8 * pb, (pk_use & 1) ^ 1, p.status, (KERNEL_ID << 16) | 11)) { ok = false; break; }
-        KSB_T(6);
-        uint8_t* prow = p_gen + pb * TILE_BYTES + row * 128;
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
-          exp_chunk(s[h], h < 2 ? sc0 : sc1, h < 2 ? c0 : c1, pk + 8 * h, acc);
-#pragma unroll
-          for (int c = 2 * h; c < 2 * h + 2; ++c)
-            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          uint32_t pk[8];
+          exp_chunk(s[h], h < 2 ? sc0 : sc1, h < 2 ? c0 : c1, pk, acc);
+          tmem_st8(tmem_s + lane_sel + 8 * h, pk);
         }
         l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
-        KSB_T(5);
-        fence_proxy_async_smem();
-        KSB_T(7);
         if (rescale && j > 0) {
-          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now); the
-          // previous tile's P.V (the other P buffer) must have finished writing O
-          if (!mbar_wait_warp(p_empty + 8 * (pb ^ 1), ((g - 1) >> 1) & 1, p.status, (KERNEL_ID << 16) | 10)) { ok = false; break; }
-          tc_fence_after();
+          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now)
           uint32_t o[4][32];
           tmem_ld32(tmem_o + lane_sel + 0, o[0]);
           tmem_ld32(tmem_o + lane_sel + 32, o[1]);
@@ -425,17 +373,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             tmem_st32(tmem_o + lane_sel + 32 * c, o[c]);
           }
-          tmem_wait_st();
         }
+        tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + 8 * pb);
-        KSB_T(8);
+        if (lane == 0) mbar_arrive(p_full);
         ++g;
       }
       if (!ok) break;
       // ---- epilogue of the work item: wait for the last P.V, normalise, store
-      if (!mbar_wait_warp(p_empty + 8 * ((g - 1) & 1), ((g - 1) >> 1) & 1, p.status, (KERNEL_ID << 16) | 12)) { ok = false; break; }
+      if (!mbar_wait_warp(o_full, wi & 1, p.status, (KERNEL_ID << 16) | 12)) { ok = false; break; }
+      ++wi;
       tc_fence_after();
       const float inv_l = (l > 0.f) ? (1.f / l) : 0.f;
       const float* vsh = p.vs + w.h * D;
@@ -457,12 +405,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       tc_fence_before();
-      KSB_T(10);
     }
-#ifdef KSB_ATTN_TIMING
-    if (warp == 4 && lane == 0)
-      for (int i = 0; i < 12; ++i) atomicAdd(&g_attn_phase_cycles[i], (unsigned long long)ph_[i]);
-#endif
   }
 
   // ------------------------------------------------------------------ common exit
@@ -478,18 +421,6 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 }  // namespace ksb
 
 using namespace ksb;
-
-#ifdef KSB_ATTN_TIMING
-extern "C" int ksb_debug_attn_phase_cycles(unsigned long long* out16, int reset) {
-  cudaDeviceSynchronize();
-  if (cudaMemcpyFromSymbol(out16, ksb::attn::g_attn_phase_cycles, 16 * sizeof(unsigned long long)) != cudaSuccess) return -2;
-  if (reset) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(ksb::attn::g_attn_phase_cycles, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
                              const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,

@@ -138,32 +138,45 @@ class PeerExchange:
         import os
 
         from . import _lib
-        # the in-switch reduction objects are not needed for plain peer stores; keep the buffers unbound from them
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_" + "MULTI" + "CAST", "1")
-        try:
-            import torch.distributed._symmetric_memory as symm
-        except Exception as e:  # pragma: no cover
-            raise _lib.KsanaB200Error(f"torch symmetric memory is unavailable: {e}") from e
+        # torch's switch for NVSwitch reduction objects: plain peer stores do not need them, and buffers that were
+        # never bound to one cannot raise NVLink faults on the other ranks if a rank dies.  It only keeps the
+        # allocation unbound; no kernel of this library issues a cluster-shared load.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         P, rank = dist.get_world_size(group), dist.get_rank(group)
         if P > 8:
             raise _lib.KsanaB200Error("the fused exchange spans at most the 8 GPUs of one box")
-        gname = (group or dist.group.WORLD).group_name
-        # allocate first (local), agree that every rank could, and only then enter the collective rendezvous:
-        # a rank that failed alone would leave the others waiting there
-        bufs, err = [], None
+
+        def agree(err, what):
+            """Every rank learns whether any rank failed `what`, so that all raise together and none is left alone
+            in the next collective."""
+            ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) != 1:
+                raise _lib.KsanaB200Error(f"fused exchange: {what} failed ({err or 'on another rank'})")
+
+        # the kernels address row l of rank r at r * L_loc + l: every rank must hold the same number of rows
+        rows = torch.tensor([L_loc, -L_loc], dtype=torch.int64, device=device)
+        dist.all_reduce(rows, op=dist.ReduceOp.MIN, group=group)
+        if int(rows[0].item()) != -int(rows[1].item()):
+            raise _lib.KsanaB200Error("fused exchange: every rank must hold the same number of token rows")
+        # import and allocate first (local), agree that every rank could, and only then enter the collective rendezvous
+        bufs, err, symm = [], None, None
         try:
+            import torch.distributed._symmetric_memory as symm
             for shape, dt in zip(cls.shapes(P, L_loc, heads), (dtype, torch.float32, dtype)):
                 bufs.append(symm.empty(shape, dtype=dt, device=device))
-        except Exception as e:
+        except Exception as e:  # noqa: BLE001  (reported through agree())
             err = e
-        ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=device)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
-        if int(ok.item()) != 1:
-            raise _lib.KsanaB200Error(f"symmetric memory could not be allocated on every rank ({err or 'another rank failed'})")
-        ptrs = []
-        for t in bufs:
-            h = symm.rendezvous(t, gname)
-            ptrs.append([int(v) for v in h.buffer_ptrs])
+        agree(err, "symmetric-memory allocation")
+        gname = (group or dist.group.WORLD).group_name
+        ptrs, err = [], None
+        try:
+            for t in bufs:
+                h = symm.rendezvous(t, gname)
+                ptrs.append([int(v) for v in h.buffer_ptrs])
+        except Exception as e:  # noqa: BLE001
+            err = e
+        agree(err, "symmetric-memory rendezvous")
         flag = torch.zeros(1, dtype=torch.float32, device=device)
 
         def barrier():

@@ -18,18 +18,24 @@ from __future__ import annotations
 import torch
 
 from . import _lib, ops
+from .casting import stochastic_rounding
 from .config import KsanaLinearBackend, backend_value
 
 FP8 = torch.float8_e4m3fn
 E4M3_MAX = 448.0
 
 
-def quantize_weight_per_channel(w: torch.Tensor):
-    """Offline per-output-channel e4m3 quantisation: s_n = absmax_k / 448, Wq = (W / s_n) -> e4m3."""
+def quantize_weight_per_channel(w: torch.Tensor, seed: int | None = None):
+    """Offline per-output-channel e4m3 quantisation: s_n = absmax_k / 448, Wq = (W / s_n) -> e4m3.
+
+    ``seed`` None rounds to nearest even; an integer rounds stochastically with a generator seeded with it
+    (``stochastic_rounding``, ksana/utils/ops.py:161-180), which keeps the expected value of a patched weight
+    unbiased when small updates are merged repeatedly."""
     wf = w.float()
     amax = wf.abs().amax(dim=-1)
     s = torch.where(amax > 0, amax / torch.full_like(amax, E4M3_MAX), torch.ones_like(amax))
-    return (wf / s[:, None]).to(FP8), s
+    scaled = wf / s[:, None]
+    return (scaled.to(FP8) if seed is None else stochastic_rounding(scaled, FP8, seed=seed)), s
 
 
 def find_fp8_info(state_dict):
@@ -139,7 +145,14 @@ class B200Fp8Linear(torch.nn.Linear):
         return weight * s
 
     def set_weight(self, weight, inplace_update=False, seed=None, **kwargs):
-        wq = (weight.float() / self.weight_scale_vector()[:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(FP8)
+        """Re-quantises ``weight`` with the scales already loaded (fp8_linear.py:145-154).  With an integer ``seed``
+        the rounding is the reference's seeded stochastic rounding; without one (the reference would fail on a
+        None seed) it is round-to-nearest-even."""
+        scaled = weight.float() / self.weight_scale_vector().to(weight.device)[:, None]
+        if seed is None:
+            wq = scaled.clamp(-E4M3_MAX, E4M3_MAX).to(FP8)
+        else:
+            wq = stochastic_rounding(scaled, FP8, seed=int(seed))
         if inplace_update:
             self.weight.data.copy_(wq)
         else:

@@ -37,14 +37,15 @@ def dequantize_weight(model_sd: dict, key: str) -> torch.Tensor:
 
 
 def merge_lora_weight(model_sd: dict, lora_sd: dict, run_dtype: torch.dtype, lora_down_key: str = ".lora_down.weight",
-                      lora_up_key: str = ".lora_up.weight", strength: float = 1.0) -> dict:
+                      lora_up_key: str = ".lora_up.weight", strength: float = 1.0, seed: int | None = None) -> dict:
     """Adds ``strength * alpha / rank * up @ down`` to every weight of ``model_sd`` the LoRA file covers, in place.
 
     e4m3 weights come back as e4m3 with a per-output-channel ``scale_weight``; other dtypes come back in
-    ``run_dtype``.  Returns ``model_sd``.
+    ``run_dtype``.  ``seed``: round the re-quantised e4m3 weights stochastically (seeded, one stream per weight:
+    ``seed`` + its position in the state dict) instead of to nearest even.  Returns ``model_sd``.
     """
     is_native_weight = any("diffusion_model." in k for k in lora_sd)
-    for key in [k for k in model_sd if k.endswith(".weight")]:
+    for index, key in enumerate([k for k in model_sd if k.endswith(".weight")]):
         down_name, up_name, alpha_name = build_lora_names(key, lora_down_key, lora_up_key, is_native_weight)
         if down_name not in lora_sd:
             continue
@@ -60,7 +61,7 @@ def merge_lora_weight(model_sd: dict, lora_sd: dict, run_dtype: torch.dtype, lor
         if value.dtype in FP8_TYPES:
             if value.dtype != torch.float8_e4m3fn:
                 raise ValueError(f"{key}: only float8_e4m3fn weights are supported, got {value.dtype}")
-            wq, s = quantize_weight_per_channel(merged)
+            wq, s = quantize_weight_per_channel(merged, seed=None if seed is None else seed + index)
             model_sd[key] = wq
             model_sd[key[: -len(".weight")] + ".scale_weight"] = s
         else:

@@ -269,6 +269,13 @@ def sage_attn_core(q8, qs, k8, ks, vt, vs, Lq, Lk, out_dtype=torch.bfloat16, til
     head slot).  Returns None then."""
     _cuda(q8, qs, k8, ks, vt, vs, tile_offsets, tile_entries, tile_order, out)
     H = q8.shape[0]
+    nq = (Lq + 127) // 128
+    if q8.shape[1] != nq * 128 or k8.shape[1] != pad128(Lk) or vt.shape[2] != pad128(Lk):
+        raise _lib.KsanaB200Error("quantised operands do not match Lq / Lk (token axis must be padded to 128)")
+    if tile_offsets is not None and (tile_offsets.numel() != nq + 1 or tile_offsets.dtype != torch.int32 or tile_entries.dtype != torch.int32):
+        raise _lib.KsanaB200Error(f"tile_offsets must hold ceil(Lq/128)+1 = {nq + 1} int32 values, got {tile_offsets.numel()}")
+    if tile_order is not None and (tile_order.numel() != nq or tile_order.dtype != torch.int32):
+        raise _lib.KsanaB200Error(f"tile_order must hold ceil(Lq/128) = {nq} int32 values, got {tile_order.numel()}")
     if peer_out is not None:
         ptrs, rows, ts, hs = peer_out
         arr = _ptr_array(ptrs)
@@ -323,6 +330,32 @@ def wan_rope_table(head_dim: int = 128, max_len: int = 1024, theta: float = 1000
             cols.append(torch.outer(pos, inv))
         ang = torch.cat(cols, dim=1)
         tab = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous()
+        _ROPE_TABLES[key] = (tab.to(device), dims[0] // 2, dims[1] // 2)
+    return _ROPE_TABLES[key]
+
+
+def comfy_rope_table(head_dim: int = 128, max_len: int = 1024, theta: float = 10000.0, dtype=torch.bfloat16, device="cuda"):
+    """(cos, sin) table of the ComfyUI RoPE formulation (``EmbedND`` / ``_comfy_rope``, ksana/utils/rope.py:151-180,
+    selected by ``rope_func="comfy"``, wan_model.py:724-741), in the same [max_len, head_dim//2, 2] layout as
+    ``wan_rope_table``.
+
+    The rotation is the same pairwise one; what differs is the arithmetic: frequencies 1 / theta**linspace(0, (d-2)/d, d/2)
+    per axis in fp64, angle = position * frequency in fp64, cos / sin rounded to fp32 and then to the model's
+    ``dtype`` -- the reference builds its 2x2 matrices in the activation dtype, so with a bf16 model the table holds
+    bf16-rounded entries.  They are stored here as fp32 values that are exactly representable in ``dtype``.
+    Positions are exact for grids up to 256 per axis in bf16 (the reference's position ids are made in ``dtype`` too).
+    """
+    key = ("comfy", head_dim, max_len, theta, dtype, str(device))
+    if key not in _ROPE_TABLES:
+        d = head_dim
+        dims = [d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6)]
+        pos = torch.arange(max_len, dtype=torch.float64)
+        cols = []
+        for dd in dims:
+            expo = torch.linspace(0, (dd - 2) / dd, steps=dd // 2, dtype=torch.float64)
+            cols.append(torch.outer(pos, 1.0 / (theta ** expo)))
+        ang = torch.cat(cols, dim=1)
+        tab = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).to(dtype).to(torch.float32).contiguous()
         _ROPE_TABLES[key] = (tab.to(device), dims[0] // 2, dims[1] // 2)
     return _ROPE_TABLES[key]
 

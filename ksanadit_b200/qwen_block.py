@@ -28,8 +28,9 @@ HEAD = 128
 
 
 class B200QwenBlock(torch.nn.Module):
-    def __init__(self, dim, num_heads, ffn_dim=None, eps=1e-6, device="cuda", dtype=torch.bfloat16):
+    def __init__(self, dim, num_heads, ffn_dim=None, eps=1e-6, device="cuda", dtype=torch.bfloat16, zero_cond_t=False):
         super().__init__()
+        self.zero_cond_t = bool(zero_cond_t)
         if dim != num_heads * HEAD:
             raise _lib.KsanaB200Error(f"head size {dim // num_heads} is not supported (only {HEAD})")
         self.dim, self.num_heads, self.eps, self.dtype = dim, num_heads, eps, dtype
@@ -135,12 +136,16 @@ class B200QwenBlock(torch.nn.Module):
         hq, hs = ops.quant_fp8_rowwise(h)
         return mlp.net[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=gate2, out=x)
 
-    def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, img_grid=None, **_):
+    def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, img_grid=None, modulate_index=None, **_):
         """hidden_states [1, Li, C] (image; under sequence parallelism this rank's Li rows of the P * Li image
         tokens, rows past the grid being padding), encoder_hidden_states [1, Lt, C] (text, replicated),
         temb [1, C]; img_grid (F, H, W) of all image tokens.  Returns (text, image) like the reference block.
         ``image_rotary_emb`` is accepted for signature compatibility; the rotation tables are rebuilt from the
-        same formula (QwenEmbedRope) for ``img_grid`` and the text length."""
+        same formula (QwenEmbedRope) for ``img_grid`` and the text length.
+
+        ``zero_cond_t`` blocks (transformer.py:171-188,206-208) take temb [2, C] = [real timestep; zero timestep]
+        and ``modulate_index`` [1, Li] in {0, 1}: every image token reads its shift / scale / gate from the row
+        its index names (the kernels take one modulation row per token), the text stream uses row 0."""
         if hidden_states.shape[0] != 1:
             raise _lib.KsanaB200Error("batch 1 only")
         if img_grid is None:
@@ -155,8 +160,16 @@ class B200QwenBlock(torch.nn.Module):
         Hl = H // P
         img_tab, txt_tab = ops.qwen_rope_tables(img_grid, Lt, device=img.device)
         st = torch.nn.functional.silu(temb)
-        mods = self._modulation(st)  # [1, 12 C]: image then text, each [mod1|mod2] x [shift|scale|gate]
-        imod = mods[0, :6 * C].view(2, 3, 1, C)
+        if st.shape[0] != (2 if self.zero_cond_t else 1) or (modulate_index is not None) != self.zero_cond_t:
+            raise _lib.KsanaB200Error("a zero_cond_t block takes temb [2, C] and a modulate_index; any other block temb [1, C] and none")
+        mods = self._modulation(st)  # [rows, 12 C]: image then text, each [mod1|mod2] x [shift|scale|gate]
+        if self.zero_cond_t:
+            index = modulate_index.reshape(-1).to(img.device, torch.int64)
+            if index.numel() != Li:
+                raise _lib.KsanaB200Error(f"modulate_index must name a row for each of the {Li} image tokens")
+            imod = mods[:, :6 * C].reshape(2, 2, 3, C).permute(1, 2, 0, 3).index_select(2, index)  # [2, 3, Li, C]
+        else:
+            imod = mods[0, :6 * C].view(2, 3, 1, C)
         tmod = mods[0, 6 * C:].view(2, 3, 1, C)
 
         # local projections: text rows first (attention.py:355-357), then this rank's image rows
@@ -184,4 +197,6 @@ class B200QwenBlock(torch.nn.Module):
             o_img = distribute.sequence_to_heads(o[Lt:]).reshape(Li, C)
         txt = self._stream_tail(txt, o_txt, tmod[0, 2], tmod[1], a.to_add_out, self.txt_mlp)
         img = self._stream_tail(img, o_img, imod[0, 2], imod[1], a.to_out[0], self.img_mlp)
+        if self.dtype == torch.float16:  # transformer.py:236-239: an overflow to inf comes back as the largest fp16
+            txt, img = txt.clamp_(-65504, 65504), img.clamp_(-65504, 65504)
         return txt.unsqueeze(0), img.unsqueeze(0)

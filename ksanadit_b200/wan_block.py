@@ -237,13 +237,18 @@ class B200WanBlock(torch.nn.Module):
     def forward(self, x, e, seq_lens=None, grid_sizes=None, freqs=None, context=None, context_lens=None, step_iter=None,
                 latent_shape=None, rope_func="default", **_):
         """x [B, L, C]; e [B, 1, 6, C] (or [B, L, 6, C]); grid_sizes [B, 3] (F, H, W); context [B, Lc, C].
-        ``freqs`` is accepted for signature compatibility; the rotation table is rebuilt from the same formula."""
-        if rope_func != "default":
-            raise _lib.KsanaB200Error("only the default (complex) RoPE formulation is implemented")
+        ``freqs`` is accepted for signature compatibility; the rotation table is rebuilt from the same formula:
+        the complex one for ``rope_func="default"``, the ComfyUI one (2x2 matrices held in the activation dtype,
+        ksana/utils/rope.py:151-212) for a name containing "comfy", as WanModel selects it (wan_model.py:743-755)."""
         if x.dtype != self.dtype:
             raise TypeError(f"block built for {self.dtype}, got {x.dtype}")
         B = x.shape[0]
-        rope = ops.wan_rope_table(HEAD, 1024, device=x.device)
+        if "comfy" in (rope_func or "default"):
+            rope = ops.comfy_rope_table(HEAD, 1024, dtype=self.dtype, device=x.device)
+        elif rope_func in (None, "default"):
+            rope = ops.wan_rope_table(HEAD, 1024, device=x.device)
+        else:
+            raise _lib.KsanaB200Error(f"unknown rope_func {rope_func!r} (default or comfy)")
         em = (self.modulation.unsqueeze(0) + e) if e.dim() == 4 else (self.modulation + e).unsqueeze(1)  # [B, 1|L, 6, C]
         em = em.to(self.dtype)
         outs = []

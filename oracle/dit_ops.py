@@ -137,6 +137,37 @@ class LinearParams:
         return Qz.fp8_linear_emulated(x, self.wq, self.sw, self.b, out_dtype=x.dtype)
 
 
+def comfy_rope_matrices(grid, head_dim=128, theta=10000.0, dtype=torch.bfloat16):
+    """``WanModel._rope_encode`` + ``EmbedND`` + ``_comfy_rope`` (wan_model.py:724-741, rope.py:151-180):
+    [L, head_dim/2, 2, 2] rotation matrices [[cos, -sin], [sin, cos]] for the (f, h, w) position of every token.
+    Position ids are made in ``dtype``, angles in fp64 from fp32 positions, matrices rounded to fp32 then ``dtype``."""
+    f, h, w = grid
+    ids = torch.zeros(f, h, w, 3, dtype=dtype)
+    ids[..., 0] += torch.linspace(0, f - 1, steps=f, dtype=dtype).reshape(-1, 1, 1)
+    ids[..., 1] += torch.linspace(0, h - 1, steps=h, dtype=dtype).reshape(1, -1, 1)
+    ids[..., 2] += torch.linspace(0, w - 1, steps=w, dtype=dtype).reshape(1, 1, -1)
+    ids = ids.reshape(-1, 3)
+    d = head_dim
+    mats = []
+    for axis, dd in enumerate([d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6)]):
+        omega = 1.0 / (theta ** torch.linspace(0, (dd - 2) / dd, steps=dd // 2, dtype=torch.float64))
+        ang = torch.einsum("n,d->nd", ids[:, axis].to(torch.float32), omega)
+        m = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1)
+        mats.append(m.reshape(*m.shape[:-1], 2, 2).to(torch.float32))
+    return torch.cat(mats, dim=-3).to(dtype)
+
+
+def apply_comfy_rope(x, grid, theta=10000.0):
+    """``apply_comfyui_rope`` (rope.py:183-212) on x [L, N, D]: out = M[..., 0] * x0 + M[..., 1] * x1 per channel pair,
+    in the dtype of the matrices (= x's), the second term through ``addcmul_``."""
+    L, N, D = x.shape
+    M = comfy_rope_matrices(grid, D, theta, x.dtype)[:L, None]  # [L, 1, D/2, 2, 2]
+    x_ = x.to(M.dtype).reshape(L, N, D // 2, 1, 2)
+    out = M[..., 0] * x_[..., 0]
+    out.addcmul_(M[..., 1], x_[..., 1])
+    return out.reshape(L, N, D).type_as(x)
+
+
 def make_linear_fn(mode):
     return (lambda lp, x: lp.fp8(x)) if mode == "fp8" else (lambda lp, x: lp.fp32(x))
 
@@ -276,28 +307,37 @@ def rmsnorm_heads(x, w, eps=1e-6):
     return rmsnorm_fp32(x, w, eps)
 
 
-def qwen_block_forward(p, img, txt, temb, img_ang, txt_ang, linear="fp8", attn="sage", eps=1e-6):
+def qwen_block_forward(p, img, txt, temb, img_ang, txt_ang, linear="fp8", attn="sage", eps=1e-6, modulate_index=None):
     """QwenImageTransformerBlock.forward (qwen/transformer.py:196-241), batch 1.
 
-    img [Li,C], txt [Lt,C], temb [C].  p holds LinearParams 'img_mod','txt_mod' (C -> 6C),
+    img [Li,C], txt [Lt,C], temb [C] -- or [2,C] = [real timestep; zero timestep] together with
+    ``modulate_index`` [Li] in {0,1} (the block's ``zero_cond_t`` mode, transformer.py:171-188,206-208:
+    every image token picks its shift / scale / gate from the row its index names, the text stream uses
+    row 0).  p holds LinearParams 'img_mod','txt_mod' (C -> 6C),
     'to_q','to_k','to_v','add_q_proj','add_k_proj','add_v_proj','to_out','to_add_out',
     'img_mlp.0','img_mlp.2','txt_mlp.0','txt_mlp.2' and fp32 [D] vectors 'norm_q','norm_k',
-    'norm_added_q','norm_added_k'.
+    'norm_added_q','norm_added_k'.  fp16 outputs are clamped to +-65504 (transformer.py:236-239).
     """
     lin = make_linear_fn(linear)
     att = make_attn_fn(attn)
     n = p["num_heads"]
     C = img.shape[-1]
     d = C // n
-    st = F.silu(temb)[None]
-    img_mod = lin(p["img_mod"], st)[0].chunk(2, dim=-1)  # every ops.Linear of the block is the FP8 Linear
-    txt_mod = lin(p["txt_mod"], st)[0].chunk(2, dim=-1)
+    st = F.silu(temb.reshape(-1, C))
+    assert (st.shape[0] == 2) == (modulate_index is not None), "two temb rows go with a modulate_index"
+    img_mod = lin(p["img_mod"], st).chunk(2, dim=-1)  # every ops.Linear of the block is the FP8 Linear
+    txt_mod = lin(p["txt_mod"], st[:1]).chunk(2, dim=-1)
 
-    def mod(x, m):  # transformer.py:171-194
+    def mod(x, m, index=None):  # transformer.py:171-194
         shift, scale, gate = m.chunk(3, dim=-1)
+        if index is None:
+            shift, scale, gate = shift[0], scale[0], gate[0]
+        else:
+            rows = index.long()
+            shift, scale, gate = shift[rows], scale[rows], gate[rows]
         return layernorm_noaffine(x, eps) * (1 + scale) + shift, gate
 
-    ih, ig1 = mod(img, img_mod[0])
+    ih, ig1 = mod(img, img_mod[0], modulate_index)
     th, tg1 = mod(txt, txt_mod[0])
     Li, Lt = img.shape[0], txt.shape[0]
     iq = rmsnorm_heads(lin(p["to_q"], ih).view(Li, n, d), p["norm_q"], eps)
@@ -315,10 +355,12 @@ def qwen_block_forward(p, img, txt, temb, img_ang, txt_ang, linear="fp8", attn="
     to, io = o[:Lt], o[Lt:]
     img = img + ig1 * lin(p["to_out"], io)
     txt = txt + tg1 * lin(p["to_add_out"], to)
-    ih, ig2 = mod(img, img_mod[1])
+    ih, ig2 = mod(img, img_mod[1], modulate_index)
     img = img + ig2 * lin(p["img_mlp.2"], gelu_tanh(lin(p["img_mlp.0"], ih)))
     th, tg2 = mod(txt, txt_mod[1])
     txt = txt + tg2 * lin(p["txt_mlp.2"], gelu_tanh(lin(p["txt_mlp.0"], th)))
+    if img.dtype == torch.float16:
+        img, txt = img.clamp(-65504, 65504), txt.clamp(-65504, 65504)
     return img, txt
 
 

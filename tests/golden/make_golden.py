@@ -264,6 +264,57 @@ def main():
     gold["qwen_block"] = dict(seed_params=5, seed_x=6, dim=qdim, ffn=qffn, heads=qheads, grid=torch.tensor(qgrid), txt=txt,
                               temb=temb, img_y=i_ref[0], txt_y=t_ref[0])
 
+    # ---- (6) seeded stochastic rounding to FP8 (utils/ops.py:131-180) ---------------------
+    from ksana.utils.ops import stochastic_rounding as ref_sr
+
+    from ksanadit_b200 import casting
+    sr = {}
+    for nm, dt, shape in (("e4m3", torch.float8_e4m3fn, (96, 64)), ("e5m2", torch.float8_e5m2, (33, 40))):
+        xs = torch.randn(*shape, generator=g) * 30
+        xs[0, :8] = torch.tensor([0, 1e-4, -1e-3, 0.0019, 500, -600, 448, 0.0156])
+        y_ref = ref_sr(xs.clone(), dt, seed=11)
+        y_own = casting.stochastic_rounding(xs.clone(), dt, seed=11)
+        assert torch.equal(y_ref.view(torch.uint8), y_own.view(torch.uint8)), nm
+        sr[nm] = dict(x=xs, seed=11, y=y_ref.view(torch.uint8))
+    print("[6] stochastic rounding: product == reference (bit-exact, e4m3 and e5m2)")
+    gold["stochastic_rounding"] = sr
+
+    # ---- (7) ComfyUI RoPE (utils/rope.py:151-212, wan_model.py:724-741) --------------------
+    from ksana.utils.rope import EmbedND, apply_comfyui_rope
+    cgrid = (3, 4, 6)
+    emb = EmbedND(dim=dd, theta=10000.0, axes_dim=[dd - 4 * (dd // 6), 2 * (dd // 6), 2 * (dd // 6)])
+    comfy = {}
+    for nm, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+        f_, h_, w_ = cgrid
+        ids = torch.zeros((f_, h_, w_, 3), dtype=dt)
+        ids[:, :, :, 0] += torch.linspace(0, f_ - 1, steps=f_, dtype=dt).reshape(-1, 1, 1)
+        ids[:, :, :, 1] += torch.linspace(0, h_ - 1, steps=h_, dtype=dt).reshape(1, -1, 1)
+        ids[:, :, :, 2] += torch.linspace(0, w_ - 1, steps=w_, dtype=dt).reshape(1, 1, -1)
+        cf = emb(ids.reshape(1, -1, 3)).movedim(1, 2).to(dtype=dt)  # WanModel._rope_encode
+        xc = torch.randn(1, f_ * h_ * w_, 2, dd, generator=g).to(dt)
+        y_ref = apply_comfyui_rope(xc, cf)
+        assert torch.equal(y_ref[0], D.apply_comfy_rope(xc[0], cgrid)), nm
+        comfy[nm] = dict(x=xc[0], grid=torch.tensor(cgrid), y=y_ref[0])
+    print("[7] ComfyUI RoPE: oracle == reference (bit-exact, bf16 and fp16)")
+    gold["comfy_rope"] = comfy
+
+    # ---- (8) Qwen block with zero_cond_t / modulate_index (qwen/transformer.py:171-188,206-208) ----
+    qz = QwenImageTransformerBlock(qdim, qheads, qdim // qheads, zero_cond_t=True, operation_settings=st)
+    qz.load_state_dict(sd, strict=False)
+    qz.eval()
+    temb2 = torch.randn(2, qdim, generator=g).to(torch.bfloat16)
+    index = (torch.rand(1, Li, generator=g) < 0.4).to(torch.int64)
+    with torch.no_grad():
+        tz_ref, iz_ref = qz(img, txt, temb2, image_rotary_emb=(vf, tf), modulate_index=index)
+    iz_or, tz_or = D.qwen_block_forward(qp, img[0], txt[0], temb2, ia, ta, linear="fp32", attn="sdpa", modulate_index=index[0])
+    di, dt_ = max_abs_rel(iz_or.float(), iz_ref[0].float()), max_abs_rel(tz_or.float(), tz_ref[0].float())
+    print(f"[8] Qwen block zero_cond_t: img max-abs-rel {di:.3e}; txt {dt_:.3e}")
+    assert di <= 1.5e-2 and dt_ <= 1.5e-2
+    with torch.no_grad():  # every token on row 0 / row 1: the per-token choice must matter
+        _, i_all0 = qz(img, txt, temb2, image_rotary_emb=(vf, tf), modulate_index=torch.zeros_like(index))
+    assert float((iz_ref != i_all0).float().mean()) > 0.2, "the index must change the image stream"
+    gold["qwen_block_zero_cond"] = dict(temb=temb2, index=index[0], img_y=iz_ref[0], txt_y=tz_ref[0])
+
     out = os.path.join(HERE, "reference_vectors.pt")
     torch.save(gold, out)
     print("wrote", out, os.path.getsize(out), "bytes")

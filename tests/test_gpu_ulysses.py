@@ -16,13 +16,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 _WORKER = r"""
-import os, sys, torch, torch.distributed as dist
+import datetime, os, sys, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
 from ksanadit_b200.wan_block import B200WanBlock
 from ksanadit_b200 import _lib
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
-dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=60))
 dim, ffn, heads, grid = 512, 1024, 4, (2, 8, 10)
 L = grid[0] * grid[1] * grid[2]
 blk = B200WanBlock(dim, ffn, heads, device="cuda").random_init(7)
@@ -69,21 +69,38 @@ def test_fused_exchange_layouts_on_one_gpu(P):
     assert (got == ref).float().mean() > 0.9
 
 
+def _run_ranks(cmds_envs, timeout=240):
+    """Starts one child per rank and waits for all of them; on any failure or timeout every child is killed and
+    reaped, so no rank is left inside a collective holding a GPU."""
+    procs = [subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for cmd, env in cmds_envs]
+    outs = []
+    try:
+        for p in procs:
+            out, _ = p.communicate(timeout=timeout)
+            outs.append(out.decode())
+            if p.returncode != 0:
+                raise AssertionError(f"rank exited with {p.returncode}:\n{outs[-1][-3000:]}")
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        for p in procs:
+            try:
+                p.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                pass
+    return outs
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("mode", ["nccl", "fused"])
 def test_wan_block_two_ranks_match_one(tmp_path, mode):
     from ksanadit_b200.wan_block import B200WanBlock
     script = tmp_path / "worker.py"
     script.write_text(_WORKER)
-    procs = []
-    for r in range(2):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29533",
-                   NCCL_NVLS_ENABLE="0")
-        procs.append(subprocess.Popen([sys.executable, str(script), ROOT, str(tmp_path), mode], env=env, stdout=subprocess.PIPE,
-                                      stderr=subprocess.STDOUT))
-    for p in procs:
-        out, _ = p.communicate(timeout=600)
-        assert p.returncode == 0, out.decode()[-3000:]
+    _run_ranks([([sys.executable, str(script), ROOT, str(tmp_path), mode],
+                 dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29533",
+                      NCCL_NVLS_ENABLE="0")) for r in range(2)])
     dim, ffn, heads, grid = 512, 1024, 4, (2, 8, 10)
     L = grid[0] * grid[1] * grid[2]
     blk = B200WanBlock(dim, ffn, heads, device="cuda").random_init(7)
@@ -99,13 +116,13 @@ def test_wan_block_two_ranks_match_one(tmp_path, mode):
 
 
 _QWEN_WORKER = r"""
-import os, sys, torch, torch.distributed as dist
+import datetime, os, sys, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
 from ksanadit_b200.qwen_block import B200QwenBlock
 from ksanadit_b200 import _lib
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
-dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=60))
 dim, heads, ffn, grid, Lt = 512, 4, 1024, (1, 8, 12), 40
 blk = B200QwenBlock(dim, heads, ffn).random_init(9)
 g = torch.Generator().manual_seed(4)
@@ -126,15 +143,9 @@ def test_qwen_block_two_ranks_match_one(tmp_path):
     from ksanadit_b200.qwen_block import B200QwenBlock
     script = tmp_path / "qworker.py"
     script.write_text(_QWEN_WORKER)
-    procs = []
-    for r in range(2):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29537",
-                   NCCL_NVLS_ENABLE="0")
-        procs.append(subprocess.Popen([sys.executable, str(script), ROOT, str(tmp_path)], env=env, stdout=subprocess.PIPE,
-                                      stderr=subprocess.STDOUT))
-    for p in procs:
-        out, _ = p.communicate(timeout=600)
-        assert p.returncode == 0, out.decode()[-3000:]
+    _run_ranks([([sys.executable, str(script), ROOT, str(tmp_path)],
+                 dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29537",
+                      NCCL_NVLS_ENABLE="0")) for r in range(2)])
     dim, heads, ffn, grid, Lt = 512, 4, 1024, (1, 8, 12), 40
     blk = B200QwenBlock(dim, heads, ffn).random_init(9)
     g = torch.Generator().manual_seed(4)
