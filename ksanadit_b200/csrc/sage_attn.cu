@@ -2,35 +2,39 @@
 //
 //   S = Q8 . K8^T            tcgen05.mma kind::i8   (s32 accumulator in tensor memory, see below)
 //   X = float(S) * qs * ks   fp32, exp2 domain (softmax scale and log2 e are folded into Q8's scale)
-//   P = exp2(X - m + 8)      fp32 online softmax against the exact running row maximum, rounded to e4m3
-//   O += P . V8              tcgen05.mma kind::f8f6f4, P read from tensor memory (f32 accumulator in tensor memory)
+//   P = exp2(X - r + 5)      fp32 online softmax against a per-row reference point r, rounded to e4m3
+//   O += P . V8              tcgen05.mma kind::f8f6f4 (f32 accumulator in tensor memory)
 //   out = O / l * vs
 //
+// Reference point: r follows the running row maximum lazily.  It moves (r = tile maximum, O and l scaled by
+// 2^(r_old - r)) only in a tile whose row maximum exceeds it by more than 3.5; otherwise the tile is processed
+// against the r it found.  P therefore never exceeds 2^(5 + 3.5) = 362 < 448, the e4m3 maximum, and after the
+// first tile of a row almost no tile pays for a rescale of O.
+//
 // One CTA works on one (head, 128-row Q block) at a time and walks that block's list of 128-token KV
-// tiles; two CTAs share an SM (256 tensor-memory columns and ~82 KB of shared memory each), so one
+// tiles; two CTAs share an SM (256 tensor-memory columns and ~113 KB of shared memory each), so one
 // CTA's softmax overlaps the other's MMAs.  Warp roles inside a CTA:
 //   warp 0      TMA producer (Q block once per work item; K and V^T tiles through 2-deep rings)
-//   warp 1      MMA issuer (single thread): S_0, then per tile  O += P_j . V_j  followed by  S_{j+1} = Q . K_{j+1}^T
+//   warp 1      MMA issuer (single thread): S = Q.K^T for tile j+1 is queued before P.V of tile j; P alternates between two shared-memory buffers
 //   warps 2,3   idle (they only donate registers)
-//   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written back with tcgen05.st over
-//               the first 32 columns of S (four scores per 32-bit column, the layout the MMA reads its A operand
-//               in), O rescaled in tensor memory in the tiles where a row maximum of the warp grew; final
-//               normalisation and store
-// P never touches shared memory: a 128 x 128 tile then reads Q, K (S = Q.K^T) and V (P.V) from shared memory and
-// nothing else, 48 KB per tile instead of the 128 KB of a shared-memory P and a copied accumulator pre-load --
-// shared-memory read bandwidth (128 B / clk), not the tensor pipe, bounded the earlier form of this kernel.
-// Because P overwrites S, S_{j+1} is issued after P_j . V_j; the barrier that announces S_{j+1} therefore also
-// says that O holds every product up to tile j, which is what the O rescale needs.
-//
+//   warps 4..7  softmax: one row per thread; tcgen05.ld S, max, exp2, e4m3 P written to shared memory
+//               in the 128-byte-swizzled K-major layout the MMA reads, O rescaled in tensor memory in the rare
+//               tiles where a reference point of the warp moved; final normalisation and store
 // The s32 score accumulator must read back as an fp32 number: every S = Q.K^T starts with one bf16 MMA
 // (A = 1 at k = 0 and 8, B = 1.5 * 2^22 at k = 0 and 8, both from constant shared-memory blocks) that writes
 // 12582912.0f = 0x4B400000 to all 128 x 128 accumulators, and the INT8 MMAs accumulate on top of those bits: taken as
 // fp32 they are exactly 12582912 + S (|S| < 2^22), so the scores need no integer-to-float conversion and
-// X = fma(bits_as_float, scale, -12582912 * scale - m + 8).
+// X - r + 5 = fma(bits_as_float, scale, -12582912 * scale - r + 5).
 // Every mbarrier wait is bounded (see common.cuh).
 //
-// Tensor-bound: 4 * 128 * 128 * 128 flop per visited (Q block, KV tile) pair; the 16 384 exp2 of a tile cost
-// 1024 cycles of the special-function unit against 512 tensor-pipe cycles, which is the practical ceiling.
+// What bounds it: the 16 384 exp2 of a tile are 1024 cycles of the special-function unit against 512 tensor-pipe
+// cycles, and special-function instructions share their issue queue with the shared-memory, barrier and
+// tensor-memory instructions of the other CTA's softmax warp on the same scheduler, so every hand-off of a warp that
+// is between two exponential phases waits behind its neighbour's exponentials.  Fewer hand-offs per tile is what
+// pays: the P buffer needs no "free" barrier (the barrier that announces S_j is committed behind the P.V of tile
+// j - 2, the buffer's last reader), and the lazy reference point removes most O rescales and their waits.
+//
+// Tensor-bound: 4 * 128 * 128 * 128 flop per visited (Q block, KV tile) pair.
 #include "../../include/ksana_b200.h"
 #include "common.cuh"
 #include "host_utils.h"
@@ -43,15 +47,17 @@ constexpr int UMMA_K = 32;
 constexpr int KST = 2, VST = 2;
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int THREADS = 256;
-constexpr int TMEM_COLS = 256;  // S: columns 0..127 (s32; P as packed e4m3 over columns 0..31), O: columns 128..255 (f32)
+constexpr int TMEM_COLS = 256;  // S: columns 0..127 (s32), O: columns 128..255 (f32)
 constexpr int KERNEL_ID = 2;
 constexpr float S_MAGIC = 12582912.0f;  // 1.5 * 2^23 = 0x4B400000: one ulp is 1 on [2^23, 2^24)
-constexpr float P_SHIFT = 8.0f;  // P carries a static factor 2^8 into e4m3: the row maximum maps to 256 exactly
-constexpr int NUM_BARS = 18;
-// Q | K x KST | V x VST | constants | barriers.  The dynamic shared memory window itself must be 1024-byte aligned
+constexpr float REF_SLACK = 3.5f;  // a row's reference point moves only when its maximum exceeds it by more than this
+constexpr float P_SHIFT = 5.0f;  // P carries a static factor 2^5 into e4m3: at most 2^(5 + REF_SLACK) = 362 is ever rounded
+constexpr int PST = 2;  // P buffers: P of tile g goes to buffer g & 1, so it never waits for the previous P.V
+constexpr int NUM_BARS = 16;
+// Q | P x PST | K x KST | V x VST | barriers.  The dynamic shared memory window itself must be 1024-byte aligned
 // (checked at kernel start): with two CTAs per SM there is no room for alignment slack.
-constexpr int NUM_TILES = 1 + KST + VST;
-constexpr int CONST_BYTES = 1024;  // two 512-byte blocks of repeated 16-byte chunks: A and B of the accumulator pre-load MMA
+constexpr int NUM_TILES = 1 + PST + KST + VST;
+constexpr int CONST_BYTES = 768;  // two 384-byte blocks of repeated 16-byte chunks: A and B of the accumulator pre-load MMA
 constexpr int SMEM_BYTES = NUM_TILES * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS + 64;
 
 struct Params {
@@ -133,15 +139,15 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* gen = smem_raw;
-  const uint32_t q_smem = base;
-  const uint32_t k_smem = base + TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
+  const uint32_t q_smem = base, p_smem = base + TILE_BYTES;
+  const uint32_t k_smem = base + (1 + PST) * TILE_BYTES, v_smem = k_smem + KST * TILE_BYTES;
   const uint32_t const_smem = v_smem + VST * TILE_BYTES;
   const uint32_t bars = const_smem + CONST_BYTES;
-  const uint32_t q_full = bars, q_empty = bars + 8, k_full = bars + 16, k_empty = bars + 16 + 8 * KST, v_full = bars + 16 + 16 * KST,
-                 v_empty = v_full + 8 * VST, s_full = v_empty + 8 * VST, p_full = s_full + 8, o_full = s_full + 16;
-  static_assert(2 + 2 * KST + 2 * VST + 3 <= NUM_BARS, "barrier block too small");
+  const uint32_t q_full = bars, q_empty = bars + 8, k_full = bars + 16, k_empty = bars + 32, v_full = bars + 48,
+                 v_empty = bars + 64, s_full = bars + 80, s_empty = bars + 88, p_full = bars + 96, p_empty = bars + 112;  // p_*: PST each
   const uint32_t tmem_slot = bars + 8 * NUM_BARS + 16;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + NUM_TILES * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS + 16);
+  uint8_t* p_gen = gen + TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total = p.H * p.nq;
@@ -156,8 +162,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int s = 0; s < KST; ++s) { mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1); }
     for (int s = 0; s < VST; ++s) { mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1); }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
-    mbar_init(o_full, 1);
+    mbar_init(s_empty, 4);  // one arrival per softmax warp (an elected lane, after the warp has synchronised)
+    for (int b = 0; b < PST; ++b) { mbar_init(p_full + 8 * b, 4); mbar_init(p_empty + 8 * b, 1); }
     fence_barrier_init();
   }
   if (threadIdx.x < CONST_BYTES / 4) {
@@ -215,22 +221,21 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = IDESC_S8_S32(BQ, BKV);
       constexpr uint32_t idesc_pv = IDESC_F8_E4M3_F32(BQ, D);
-      constexpr uint32_t idesc_pre = IDESC_BF16_F32(BQ, BKV);
       const uint64_t dq = make_kmajor_sw128_desc(q_smem);
+      constexpr uint32_t idesc_pre = IDESC_BF16_F32(BQ, BKV);
       // constant blocks: every 16-byte chunk of a block is the same, so only the footprint of the descriptors
-      // matters -- core matrices 16 B apart in both directions stay inside the 512-byte block
+      // matters -- core matrices 16 B apart in both directions stay inside the 384-byte block
       const uint64_t dca = make_noswizzle_desc(const_smem, 16, 16);
       const uint64_t dcb = make_noswizzle_desc(const_smem + CONST_BYTES / 2, 16, 16);
       uint32_t wi = 0, itk = 0, itv = 0, g = 0;
       bool ok = true;
-      // S = 12582912 + Q.K^T for the next K tile of the ring; the caller guarantees that the softmax warps are done
-      // with the previous S and that every MMA reading the previous P has been issued
-      auto issue_qk = [&]() -> bool {
+      auto issue_qk = [&](uint32_t gg) -> bool {
         const uint32_t s = itk % KST, ph = (itk / KST) & 1;
         if (!mbar_wait(k_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 4)) return false;
+        if (!mbar_wait(s_empty, gg & 1, p.status, (KERNEL_ID << 16) | 5)) return false;  // S read by the softmax warps (completion #gg)
         tc_fence_after();
         const uint64_t dk = make_kmajor_sw128_desc(k_smem + s * TILE_BYTES);
-        mma_bf16_ss(tmem_s, dca, dcb, idesc_pre, 0);
+        mma_bf16_ss(tmem_s, dca, dcb, idesc_pre, 0);  // every accumulator = 12582912.0f
 #pragma unroll
         for (int kk = 0; kk < D / UMMA_K; ++kk) mma_i8_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_qk, 1);  // on top of the pre-load
         mma_commit(s_full);
@@ -242,25 +247,26 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const Work w = get_work(p, idx);
         if (w.n == 0) continue;
         if (!mbar_wait(q_full, wi & 1, p.status, (KERNEL_ID << 16) | 6)) { ok = false; break; }
-        if (!issue_qk()) { ok = false; break; }
-        if (w.n == 1) mma_commit(q_empty);  // the work item's last S = Q.K^T has been issued: Q may be replaced once it completes
+        if (!issue_qk(g)) { ok = false; break; }
         for (int j = 0; j < w.n; ++j) {
+          if (j + 1 < w.n) {
+            if (!issue_qk(g + 1)) { ok = false; break; }
+          } else {
+            mma_commit(q_empty);  // every S = Q.K^T of this work item has been issued
+          }
           const uint32_t s = itv % VST, ph = (itv / VST) & 1;
           if (!mbar_wait(v_full + 8 * s, ph, p.status, (KERNEL_ID << 16) | 7)) { ok = false; break; }
-          if (!mbar_wait(p_full, g & 1, p.status, (KERNEL_ID << 16) | 8)) { ok = false; break; }
+          const uint32_t pb = g & 1, pph = (g >> 1) & 1;
+          if (!mbar_wait(p_full + 8 * pb, pph, p.status, (KERNEL_ID << 16) | 8)) { ok = false; break; }
+          const uint64_t dp = make_kmajor_sw128_desc(p_smem + pb * TILE_BYTES);
           tc_fence_after();
           const uint64_t dv = make_kmajor_sw128_desc(v_smem + s * TILE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BKV / UMMA_K; ++kk) mma_f8_ts(tmem_o, tmem_s + 8 * kk, dv + 2 * kk, idesc_pv, (j | kk) != 0);
+          for (int kk = 0; kk < BKV / UMMA_K; ++kk) mma_f8_ss(tmem_o, dp + 2 * kk, dv + 2 * kk, idesc_pv, (j | kk) != 0);
+          mma_commit(p_empty + 8 * pb);
           mma_commit(v_empty + 8 * s);
           ++itv;
           ++g;
-          if (j + 1 < w.n) {
-            if (!issue_qk()) { ok = false; break; }
-            if (j + 2 == w.n) mma_commit(q_empty);
-          } else {
-            mma_commit(o_full);  // every P.V of this work item has completed: O is final
-          }
         }
         ++wi;
       }
@@ -273,8 +279,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t lane_sel = static_cast<uint32_t>(qrt * 32) << 16;
     const int nk64 = p.nkv * 2;
     T* out = static_cast<T*>(p.out);
-    uint32_t g = 0, wi = 0;
+    uint32_t g = 0;
     bool ok = true;
+    // the score accumulator is free for the first S = Q.K^T (completion #0 of s_empty)
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_empty);
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
       const Work w = get_work(p, idx);
       const int qrow = w.qt * BQ + row;
@@ -293,7 +303,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         continue;
       }
       const float qsc = p.qs[w.h * p.nq + w.qt];
-      float m_used = -INFINITY, l = 0.f;
+      float m_ref = -INFINITY, l = 0.f;
       // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
       int e_next = entry_at(w, 0);
       float ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)], ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
@@ -308,7 +318,6 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int t = e >> 2, halves = e & 3;
         const int valid = min(BKV, p.Lk - t * BKV);
         const bool full = (halves == 3) && (valid == BKV);
-        // S_j is complete, and so is every P.V up to tile j - 1 (issued before it)
         if (!mbar_wait_warp(s_full, g & 1, p.status, (KERNEL_ID << 16) | 9)) { ok = false; break; }
         tc_fence_after();
         uint32_t s[4][32];
@@ -317,6 +326,10 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld32(tmem_s + lane_sel + 64, s[2]);
         tmem_ld32(tmem_s + lane_sel + 96, s[3]);
         tmem_wait_ld();
+        // the scores are in registers: hand the accumulator back to the MMA issuer
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty);
         if (!full) {
           // masked columns (ragged tail or dropped 64-token half) become -inf: never the maximum, P = 0
 #pragma unroll
@@ -330,32 +343,41 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         // exact: both operands of the subtraction are integers below 2^24
         const float m_tile = fmaxf((tree_max64(s[0], s[1]) - S_MAGIC) * sc0, (tree_max64(s[2], s[3]) - S_MAGIC) * sc1);
-        // The reference point is the exact running maximum: O and l are rescaled in every tile in which some
-        // row of the warp found a larger score (rows that did not get the factor 1).
-        const bool grow = m_tile > m_used;  // also true for the first tile with a valid score (m_used = -inf)
+        // The reference point moves only for a row whose tile maximum outgrew it by more than the slack; O and l are
+        // rescaled in the tiles in which that happened to some row of the warp (the other rows get the factor 1).
+        const bool grow = m_tile > m_ref + REF_SLACK;  // also true for the first tile with a valid score (m_ref = -inf)
         const bool rescale = __any_sync(0xffffffffu, grow);
         float alpha = 1.f;
         if (rescale) {
-          const float m_new = fmaxf(m_used, m_tile);
-          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+          const float m_new = grow ? m_tile : m_ref;
+          alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
           l *= alpha;
-          m_used = m_new;
+          m_ref = m_new;
         }
-        // P = exp2(X - m_used + 8) -> e4m3, packed 4 per word; masked columns give exactly 0.  Each 32-score chunk
-        // goes back to tensor memory as soon as it is packed: 8 columns of this warp's own lanes, over scores the
-        // warp already holds in registers.
-        const float neg_m = (m_used == -INFINITY) ? 0.f : (P_SHIFT - m_used);
+        // P = exp2(X - m_ref + 5) -> e4m3, packed 4 per word; masked columns give exactly 0
+        const float neg_m = (m_ref == -INFINITY) ? 0.f : (P_SHIFT - m_ref);
+        uint32_t pk[32];
         float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         const float c0 = fmaf(-S_MAGIC, sc0, neg_m), c1 = fmaf(-S_MAGIC, sc1, neg_m);
+        // This tile's P buffer was last read by the P.V of two tiles ago, and that P.V has completed: S_j was issued
+        // behind it and the barrier awaited above covers everything issued before S_j.  Each 32-score chunk is stored
+        // as soon as it is packed (row `row` of the K-major tile: 16-byte chunks, chunk index XORed with (row & 7)).
+        const uint32_t pb = g & 1;
+        uint8_t* prow = p_gen + pb * TILE_BYTES + row * 128;
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
-          uint32_t pk[8];
-          exp_chunk(s[h], h < 2 ? sc0 : sc1, h < 2 ? c0 : c1, pk, acc);
-          tmem_st8(tmem_s + lane_sel + 8 * h, pk);
+          exp_chunk(s[h], h < 2 ? sc0 : sc1, h < 2 ? c0 : c1, pk + 8 * h, acc);
+#pragma unroll
+          for (int c = 2 * h; c < 2 * h + 2; ++c)
+            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         }
         l += ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+        fence_proxy_async_smem();
         if (rescale && j > 0) {
-          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now)
+          // O *= alpha with all four 32-column chunks in flight (the score registers are dead by now); the
+          // previous tile's P.V (the other P buffer) must have finished writing O
+          if (!mbar_wait_warp(p_empty + 8 * (pb ^ 1), ((g - 1) >> 1) & 1, p.status, (KERNEL_ID << 16) | 10)) { ok = false; break; }
+          tc_fence_after();
           uint32_t o[4][32];
           tmem_ld32(tmem_o + lane_sel + 0, o[0]);
           tmem_ld32(tmem_o + lane_sel + 32, o[1]);
@@ -373,17 +395,16 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             tmem_st32(tmem_o + lane_sel + 32 * c, o[c]);
           }
+          tmem_wait_st();
         }
-        tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full);
+        if (lane == 0) mbar_arrive(p_full + 8 * pb);
         ++g;
       }
       if (!ok) break;
       // ---- epilogue of the work item: wait for the last P.V, normalise, store
-      if (!mbar_wait_warp(o_full, wi & 1, p.status, (KERNEL_ID << 16) | 12)) { ok = false; break; }
-      ++wi;
+      if (!mbar_wait_warp(p_empty + 8 * ((g - 1) & 1), ((g - 1) >> 1) & 1, p.status, (KERNEL_ID << 16) | 12)) { ok = false; break; }
       tc_fence_after();
       const float inv_l = (l > 0.f) ? (1.f / l) : 0.f;
       const float* vsh = p.vs + w.h * D;

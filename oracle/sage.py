@@ -7,19 +7,22 @@ Arithmetic (the build's contract; the reference delegates it to the un-vendored
   Q8, qs  = int8 blocks of 128 tokens of  Q * (D^-1/2 * log2 e)
   K8, ks  = int8 blocks of  64 tokens of  K - km
   V8, vs  = e4m3 per (head, channel) over tokens
-  per 128-row Q block, KV tiles of 128 tokens visited in ascending order:
+  per 128-row Q block, KV tiles of 128 tokens visited in ascending order, per row:
       X   = float(Q8 . K8^T) * (qs * ks)                      int32 dot, fp32 scale
-      m'  = max(m, rowmax X);  P = exp2(X - m' + 8);  a = exp2(m - m')
-      l   = l * a + rowsum(P)                                 fp32, P before rounding
-      O   = O * a + float(e4m3(P)) . float(V8)                fp32 accumulate
+      if rowmax X > r + 3.5:  a = exp2(r - rowmax X);  r = rowmax X;  l = l * a;  O = O * a
+      P   = exp2(X - r + 5)
+      l   = l + rowsum(P)                                     fp32, P before rounding
+      O   = O + float(e4m3(P)) . float(V8)                    fp32 accumulate
   out = O / l * vs  -> input dtype
 
-P carries a fixed factor 2^8 (P_SHIFT): the row's largest P is exactly 256, which e4m3 holds
-exactly, and the bulk of a long, flat attention row lands in e4m3's normal range instead of its
-subnormals (the published SageAttention2 recipe scales P by a static factor for the same reason);
-the factor cancels in O / l.  The reference point m is the exact running row maximum, updated
-at every tile in which it grows -- an implementation has to rescale O at exactly those tiles to
-round P on the same e4m3 grid.
+The reference point r of a row (initially -inf, so the first valid score always sets it) follows the running
+row maximum lazily: it moves only when a tile's maximum exceeds it by more than REF_SLACK = 3.5 (a factor 11.3).
+P carries a fixed factor 2^5 (P_SHIFT), so the largest value ever rounded to e4m3 is below 2^8.5 = 362 < 448,
+and the bulk of a long, flat attention row lands in e4m3's normal range instead of its subnormals (the published
+SageAttention2 recipe scales P by a static factor for the same reason); the factor cancels in O / l.  An
+implementation has to move r at exactly those tiles to round P on the same e4m3 grid; after the first tile of a
+row that is rare, which is the point: O is rescaled in few tiles, and the exponentials of a tile do not have to
+wait for its row maximum.
 
 Block-sparse variant: a tile mask [ceil(Lq/128), ceil(Lk/64)] (the reference's
 ``mask_id`` granularity, radial_sage_attn.py:155-160,174) removes whole
@@ -33,7 +36,8 @@ import torch.nn.functional as F
 
 from . import quantizers as Qz
 
-P_SHIFT = 8.0  # log2 of the static scale applied to P before the e4m3 rounding
+P_SHIFT = 5.0  # log2 of the static scale applied to P before the e4m3 rounding
+REF_SLACK = 3.5  # a row's reference point moves only when the tile maximum exceeds it by more than this
 
 
 def sdpa_reference(q, k, v, sm_scale=None):
@@ -77,10 +81,12 @@ def sage_core(pp, Lq, Lk, tile_mask=None, out_dtype=torch.float32):
             tm = tile_mask[:, 2 * j : 2 * j + 2].to(torch.bool).repeat_interleave(64, dim=1)  # [nq,128]
             valid = valid & tm[None, :, None, :]
         X = torch.where(valid, X, torch.full_like(X, float("-inf")))
-        m_new = torch.maximum(m, X.amax(dim=-1))
+        m_tile = X.amax(dim=-1)
+        move = m_tile > m + REF_SLACK  # true for the first valid score of a row (m = -inf), never for a fully masked tile
+        m_new = torch.where(move, m_tile, m)
         safe = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
         P = torch.exp2(X - safe[..., None] + P_SHIFT)
-        a = torch.exp2(torch.where(torch.isinf(m), torch.full_like(m, float("-inf")), m - safe))
+        a = torch.where(move, torch.exp2(torch.where(torch.isinf(m), torch.full_like(m, float("-inf")), m - safe)), torch.ones_like(m))
         l = l * a + P.sum(dim=-1)
         P8 = P.to(torch.float8_e4m3fn).float()
         vt = vf[:, :, j * 128 : (j + 1) * 128]  # [H,D,128]
