@@ -31,9 +31,13 @@ sys.path.insert(0, ROOT)
 
 # Wan2.2-T2V-14B block stack (ksana/settings/wan/modules/14b.yaml:16-26) at 720p x 81 frames
 W14 = dict(layers=40, dim=5120, ffn=13824, heads=40, grid=(21, 45, 80), text_len=512)
-# DRAM bytes (read + write) of one self-attention launch per head at 75 600 tokens, from the one-pass ncu capture of
-# the full-size launch summarised in profiles/sage_attn_kernel_L16384_H16_and_full.md (3.26 GB for 40 heads)
+# DRAM bytes (read + write) of one self-attention launch per head at 75 600 tokens.  Not measured by this script: the
+# figure comes from a separate one-pass profiler capture (dram__bytes_read.sum + dram__bytes_write.sum) of a launch
+# with 8 heads of this shape, divided by the head count (every head reads its own Q, K and V and writes its own
+# output rows, so the bytes per head do not depend on how many heads a launch has); `roofline.traffic_source` says so.
 ATTN_DRAM_BYTES_PER_HEAD = 3.262e9 / 40
+ATTN_TRAFFIC_SOURCE = ("profiler capture of one 75600-token launch (DRAM read + write counters), scaled by the head count; "
+                       "not measured in this run")
 METRIC = "wan14b_dit_step_tflops"
 UNIT = "TFLOP/s"
 
@@ -89,23 +93,178 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def measure_fp8_peak(device):
-    """Dense FP8 tensor peak measured the way MEASURED_PEAKS.json measures bf16: torch._scaled_mm e4m3 8192^3, best of 10."""
+def measure_fp8_peak(device, sustained_seconds=4.0):
+    """Dense FP8 tensor peak measured the way MEASURED_PEAKS.json measures bf16: torch._scaled_mm e4m3 8192^3, best of 10
+    (burst) and back to back for `sustained_seconds` under the power cap (sustained).  Returns (burst, sustained) TFLOP/s."""
     n = 8192
     a = torch.randn(n, n, device=device).clamp(-2, 2).to(torch.float8_e4m3fn)
     b = torch.randn(n, n, device=device).clamp(-2, 2).to(torch.float8_e4m3fn)
     one = torch.ones((), device=device)
     best = float("inf")
-    for _ in range(3):
+
+    def mm():
         torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+    for _ in range(3):
+        mm()
     for _ in range(10):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        mm()
         e1.record()
         torch.cuda.synchronize()
         best = min(best, e0.elapsed_time(e1))
-    return 2.0 * n ** 3 / best / 1e9
+    reps = max(10, int(sustained_seconds * 1e3 / best))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        mm()
+    e1.record()
+    torch.cuda.synchronize()
+    return 2.0 * n ** 3 / best / 1e9, 2.0 * n ** 3 * reps / e0.elapsed_time(e1) / 1e9
+
+
+def _median_ms(fn, iters=5, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def secondary_measurements(dev):
+    """The benchmark's other configurations, measured outside the timed region on one GPU (CUDA events, median of 5):
+    the four Linears of the step beside the library call the reference makes for them, dense attention beside the
+    box's bf16 library attention, the frame-masked block-sparse attention beside dense, and the Qwen-Image-shaped step."""
+    from ksanadit_b200 import _lib, ops, radial_mask
+    from ksanadit_b200.qwen_block import B200QwenBlock
+    out = {}
+    M = 75600
+    # ---- configuration 2: FP8 Linear sweep (per-token x per-channel scales, the step's epilogues)
+    lin = {}
+    for name, K, N, epi in (("qkv", 5120, 15360, _lib.EPI_NONE), ("o_proj", 5120, 5120, _lib.EPI_GATE_RESIDUAL),
+                            ("ffn_up", 5120, 13824, _lib.EPI_GELU_TANH), ("ffn_down", 13824, 5120, _lib.EPI_GATE_RESIDUAL)):
+        xq = (torch.randn(M, K, device=dev) * 50).clamp(-448, 448).to(torch.float8_e4m3fn)
+        wq = (torch.randn(N, K, device=dev) * 50).clamp(-448, 448).to(torch.float8_e4m3fn)
+        sx, sw = torch.rand(M, device=dev) + 0.5, (torch.rand(N, device=dev) + 0.5) * 5e-6
+        bias = torch.randn(N, device=dev).to(torch.bfloat16)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        resid = torch.randn(M, N, device=dev).to(torch.bfloat16) if epi == _lib.EPI_GATE_RESIDUAL else None
+        gate = torch.randn(1, N, device=dev).to(torch.bfloat16) if epi == _lib.EPI_GATE_RESIDUAL else None
+        fl = 2.0 * M * N * K
+        t = _median_ms(lambda: ops.fp8_gemm(xq, sx, wq, sw, bias, epilogue=epi, resid=resid, gate=gate, out=y))
+        one = torch.ones((), device=dev)
+        t_pt = _median_ms(lambda: torch._scaled_mm(xq, wq.t(), scale_a=one, scale_b=one, bias=bias, out_dtype=torch.bfloat16))
+        t_rw = _median_ms(lambda: torch._scaled_mm(xq, wq.t(), scale_a=sx[:, None], scale_b=sw[None, :], bias=bias, out_dtype=torch.bfloat16))
+        lin[name] = {"M": M, "N": N, "K": K, "epilogue": ("none", "gelu_tanh", "gate_residual")[epi], "ms": t, "tflops": fl / t / 1e9,
+                     "torch_scaled_mm_per_tensor_ms": t_pt, "torch_scaled_mm_per_tensor_tflops": fl / t_pt / 1e9,
+                     "torch_scaled_mm_rowwise_ms": t_rw, "torch_scaled_mm_rowwise_tflops": fl / t_rw / 1e9}
+        del xq, wq, y, resid
+    out["config2_fp8_linear"] = lin
+    # ---- configurations 3 / 5: attention at 75 600 tokens x 40 heads, dense, block-sparse, and the bf16 library call
+    L, H = 75600, 40
+    q, k, v = (torch.randn(L, H, 128, device=dev).to(torch.bfloat16) for _ in range(3))
+    km = ops.sage_kmean(k)
+    q8, qs = ops.sage_quant_int8(q, 128, premul=ops.q_premul(128))
+    k8, ks = ops.sage_quant_int8(k, 64, mean=km)
+    vt, vs = ops.sage_quant_v(v)
+    o = torch.empty(L, H, 128, dtype=torch.bfloat16, device=dev)
+    fl = 4.0 * H * L * L * 128
+    t_dense = _median_ms(lambda: ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, out=o), iters=3, warmup=1)
+    m = radial_mask.bernoulli_frame_tile_mask(L, 3600, seed=0)
+    offs, ents = radial_mask.compact_tile_lists(radial_mask.expand_to_kernel_granularity(m, 128))
+    offs_d, ents_d = torch.from_numpy(offs).to(dev), torch.from_numpy(ents).to(dev)
+    t_sparse = _median_ms(lambda: ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, tile_offsets=offs_d, tile_entries=ents_d, out=o), iters=3, warmup=1)
+    qq, kk, vv = (x.permute(1, 0, 2)[None] for x in (q, k, v))
+    t_sdpa = _median_ms(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv), iters=3, warmup=1)
+    out["config3_attention"] = {"tokens": L, "heads": H, "ms": t_dense, "tflops": fl / t_dense / 1e9,
+                                "torch_sdpa_bf16_ms": t_sdpa, "torch_sdpa_bf16_tflops": fl / t_sdpa / 1e9}
+    out["config5_block_sparse"] = {"tile_density": float(m.mean()), "mask": "same-frame tiles kept, cross-frame kept with probability 2^-|dframe| (seed 0)",
+                                   "dense_ms": t_dense, "sparse_ms": t_sparse, "speedup": t_dense / t_sparse,
+                                   "speedup_if_proportional": 1.0 / float(m.mean())}
+    del q, k, v, q8, k8, vt, o, qq, kk, vv
+    # ---- configuration 4: Qwen-Image-20B-shaped step, 60 dual-stream blocks
+    dim, heads, ffn, grid, Lt, layers = 3072, 24, 12288, (1, 83, 83), 256, 60
+    blocks = [B200QwenBlock(dim, heads, ffn, device=dev).random_init(100 + i) for i in range(layers)]
+    Li = grid[1] * grid[2]
+    img = torch.randn(1, Li, dim, device=dev).to(torch.bfloat16)
+    txt = torch.randn(1, Lt, dim, device=dev).to(torch.bfloat16)
+    temb = torch.randn(1, dim, device=dev).to(torch.bfloat16)
+
+    def qstep():
+        t_, i_ = txt, img
+        for b in blocks:
+            t_, i_ = b(i_, t_, temb, img_grid=grid)
+        return i_
+
+    Lj = Li + Lt
+    qfl = layers * (2.0 * Lj * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * Lj * Lj * 128)
+    tq = _median_ms(qstep, iters=5, warmup=2)
+    out["config4_qwen_image_step"] = {"blocks": layers, "dim": dim, "heads": heads, "image_tokens": Li, "text_tokens": Lt, "ms": tq,
+                                      "tflops": qfl / tq / 1e9, "step_pflop": qfl / 1e15}
+    del blocks
+    torch.cuda.empty_cache()
+    return out
+
+
+def exchange_check(world, rank, dev):
+    """Output check carried in the benchmark line.  One rank: a small Wan-shaped block against the CPU oracle.  Several
+    ranks: a 2-block, 4096-token step of the benchmark's width through the fused exchange and through the NCCL
+    all-to-alls on the same inputs -- the only comparison the multi-GPU fused path gets outside the tests."""
+    import torch.distributed as dist
+
+    from ksanadit_b200 import _lib
+    from ksanadit_b200.wan_block import B200WanBlock, B200WanDenoiseStep
+
+    def stats(a, b):
+        a, b = a.flatten().double(), b.flatten().double()
+        return float((a @ b) / (a.norm() * b.norm() + 1e-30)), float((a - b).abs().max() / (b.abs().max() + 1e-30))
+
+    if world == 1:
+        from __graft_entry__ import block_state_dict
+        from oracle import dit_ops as D
+        dim, ffn, heads, grid = 256, 768, 2, (2, 6, 8)
+        L = grid[0] * grid[1] * grid[2]
+        p = D.make_wan_block_params(dim, ffn, heads, seed=0)
+        x = D.make_activations(L, dim, seed=0)[None]
+        g = torch.Generator().manual_seed(0)
+        e = (torch.randn(1, 1, 6, dim, generator=g) * 0.1).to(torch.bfloat16)
+        ctx = torch.randn(1, 40, dim, generator=g).to(torch.bfloat16)
+        ref = D.wan_block_forward(p, x, e, ctx, grid, linear="fp8", attn="sage").float()
+        blk = B200WanBlock(dim, ffn, heads, device=dev).load_block_state_dict(block_state_dict(p))
+        out = blk(x.to(dev), e.to(dev), grid_sizes=[grid], context=ctx.to(dev)).float().cpu()
+        c, m = stats(out, ref)
+        return {"against": "CPU oracle (FP8 Linear + Sage attention), one 256-wide block on 96 tokens", "cos": c, "max_abs_rel": m}
+    from ksanadit_b200.distribute import PeerExchange
+    cfg = W14
+    grid = (2, 32, 64)
+    L = grid[0] * grid[1] * grid[2]
+    Ll = L // world
+    model = B200WanDenoiseStep(2, cfg["dim"], cfg["ffn"], cfg["heads"], device=dev, seed=77)
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(1, Ll, cfg["dim"], generator=g).to(torch.bfloat16).to(dev)
+    gs = torch.Generator().manual_seed(5)
+    e = (torch.randn(1, 1, 6, cfg["dim"], generator=gs) * 0.1).to(torch.bfloat16).to(dev)
+    ctx = torch.randn(1, 64, cfg["dim"], generator=gs).to(torch.bfloat16).to(dev)
+    y_nccl = model(x, e, [grid], ctx).float()
+    try:
+        model.use_peer_exchange(PeerExchange.symmetric(Ll, cfg["heads"], torch.bfloat16, dev))
+    except _lib.KsanaB200Error as err:
+        return {"against": "NCCL all-to-all path", "unavailable": str(err)}
+    y_fused = model(x, e, [grid], ctx).float()
+    torch.cuda.synchronize()
+    c, m = stats(y_fused, y_nccl)
+    t = torch.tensor([-c, m], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"against": f"NCCL all-to-all path, same inputs: 2 blocks of the benchmark's width, {L} tokens over {world} ranks (worst rank)",
+            "cos": -float(t[0].item()), "max_abs_rel": float(t[1].item())}
 
 
 def cpu_reference_sample(tokens, reps):
@@ -132,6 +291,27 @@ def cpu_reference_sample(tokens, reps):
     desc = (f"one Wan2.2-14B-shaped block (dim {cfg['dim']}, ffn {cfg['ffn']}, {cfg['heads']} heads) on {tokens} tokens + "
             f"{cfg['text_len']} text tokens, torch CPU, emulated per-token/per-channel FP8 Linear + SDPA, median of {reps}")
     return fl / t / 1e12, t, desc
+
+
+def cpu_config1_block():
+    """The benchmark's CPU-runnable configuration timed whole: one Wan2.1-1.3B-shaped block (dim 1536, 12 heads, FFN 8960,
+    1560 tokens, 512 text tokens) through the CPU restatement of the reference path, all host cores."""
+    from oracle import dit_ops as D
+    dim, ffn, heads, grid = 1536, 8960, 12, (1, 30, 52)
+    p = D.make_wan_block_params(dim, ffn, heads, seed=0)
+    x = D.make_activations(1560, dim, seed=0)[None]
+    g = torch.Generator().manual_seed(0)
+    e = (torch.randn(1, 1, 6, dim, generator=g) * 0.1).to(torch.bfloat16)
+    ctx = torch.randn(1, 512, dim, generator=g).to(torch.bfloat16)
+    ts = []
+    with torch.no_grad():
+        for _ in range(3):
+            t0 = time.perf_counter()
+            D.wan_block_forward(p, x, e, ctx, grid, linear="fp8", attn="sdpa")
+            ts.append(time.perf_counter() - t0)
+    fl = step_flops(dict(layers=1, dim=dim, ffn=ffn, heads=heads, text_len=512), 1560)
+    t = statistics.median(ts)
+    return {"ms": t * 1e3, "tflops": fl / t / 1e12, "gflop": fl / 1e9}
 
 
 def run_reference(args):
@@ -257,6 +437,10 @@ def run_ours(args):
         clocks = sampler.stop() if rank == 0 else None
         step_e2e()  # one untimed pass so that the context-K/V cache state matches the resident loop
         ms_e2e = timed(step_e2e, args.steps)
+        _lib.assert_device_ok()
+        check = exchange_check(world, rank, dev)
+        _lib.assert_device_ok()
+        secondary = secondary_measurements(dev) if (world == 1 and rank == 0 and not args.no_secondary) else None
     _lib.assert_device_ok()
 
     # roofline of the dominant kernel: the self-attention launches (tensor bound)
@@ -274,7 +458,7 @@ def run_ours(args):
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except Exception:
             pass
-        fp8_peak = measure_fp8_peak(dev)
+        fp8_peak, fp8_sustained = measure_fp8_peak(dev)
         cpu_v, cpu_t, cpu_desc = cpu_reference_sample(args.cpu_tokens, 2)
         out = {
             "metric": METRIC, "value": flops * args.steps / ms / 1e9, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -292,16 +476,24 @@ def run_ours(args):
             "gpu_launches": launches,
             "roofline": {"kernel": "sage_attn_kernel (self-attention)", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
                          "unit": "TFLOP/s", "frac": (achieved / fp8_peak) if achieved else None,
+                         "peak_sustained": fp8_sustained, "frac_of_sustained": (achieved / fp8_sustained) if achieved else None,
                          "traffic": ATTN_DRAM_BYTES_PER_HEAD * Hl if L == 75600 else None,
+                         "traffic_source": ATTN_TRAFFIC_SOURCE if L == 75600 else None,
                          "algorithmic_flop_per_launch": att_flop,
-                         "peak_source": "of measured: torch._scaled_mm e4m3 8192^3 best of 10 in this run (MEASURED_PEAKS.json holds "
-                                        f"bf16 only: {peaks.get('bf16_tflops')} TF/s burst)",
+                         "peak_source": "of measured: torch._scaled_mm e4m3 8192^3 in this run, best of 10 (peak) and 4 s back to back "
+                                        f"(peak_sustained); MEASURED_PEAKS.json holds bf16 only: {peaks.get('bf16_tflops')} TF/s burst, "
+                                        f"{peaks.get('bf16_tflops_sustained')} sustained",
                          "launches": n_att, "ms_per_launch": (ms_att / n_att) if n_att else None,
                          "share_of_step": (ms_att / ms) if ms else None,
                          "gemm": {"tflops": gemm_fl / gemm_ms / 1e9 if gemm_ms else None, "share_of_step": gemm_ms / ms if ms else None}},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_desc,
-                             "sec_per_block_sample": cpu_t},
+                             "sec_per_block_sample": cpu_t, "config1_block": cpu_config1_block()},
+            "exchange_check": check,
+            "value_frac_of_fp8_peak": flops * args.steps / ms / 1e9 / fp8_peak / world,
+            "value_frac_of_fp8_sustained": flops * args.steps / ms / 1e9 / fp8_sustained / world,
         }
+        if secondary is not None:
+            out["secondary"] = secondary
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
@@ -318,6 +510,7 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "fused"],
                     help="Ulysses exchange at N > 1: NCCL all-to-alls, or peer stores fused into the GEMM / attention output stages")
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations measured after the timed region (1 GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

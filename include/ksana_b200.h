@@ -47,9 +47,17 @@ typedef void* ksb_stream_t;
 int ksb_version(void);
 const char* ksb_last_error(void);
 /* Synchronises the device, returns the status words written by kernels whose bounded waits ran out
- * (code 0 = none) and clears them. */
+ * (code 0 = none; code 1 = a wait timed out, detail = kernel id << 16 | wait site) and clears them.
+ * The words are sticky: from the moment a wait has run out, every later wait of every kernel on that GPU gives
+ * up at once and leaves its outputs unwritten, until this call has read the words.  A caller that consumes
+ * results should therefore check once per step, at a point where it synchronises anyway. */
 int ksb_device_status(int* code, int* detail);
 int ksb_sm_count(void);
+/* Diagnostic with no counterpart in KsanaDiT: launches one small kernel in which a thread waits, for at most
+ * limit_ns (<= 1e9), on a barrier that nothing ever completes.  The kernel must return by itself, store 2 in
+ * *returned (device int; 1 would mean the wait succeeded) and leave (1, 15 << 16 | 1) in the status words;
+ * the next launch on the GPU must work.  Used by the tests to exercise the time-out path without faulting a GPU. */
+int ksb_selftest_bounded_wait(int64_t limit_ns, int* returned, ksb_stream_t stream);
 
 /* Per-token FP8 activation quantiser.
  * Replaces the eager `(input * (1.0 / scale_input).to(dtype)).to(float8_e4m3fn)` pass of

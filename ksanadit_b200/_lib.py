@@ -21,6 +21,7 @@ SIGNATURES = {
     "ksb_last_error": (c_char_p, []),
     "ksb_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
     "ksb_sm_count": (c_int, []),
+    "ksb_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "ksb_quant_fp8_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ksb_quant_fp8_static": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ksb_adaln_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int, c_float,
@@ -81,7 +82,10 @@ def check(rc: int, what: str):
 
 
 def device_status():
-    """Synchronises and returns (code, detail) of the kernels' bounded-wait status words."""
+    """Synchronises and returns (code, detail) of the kernels' bounded-wait status words, clearing them.
+
+    The words are sticky: after one wait has run out, later kernels give up their waits at once (and leave their
+    outputs unwritten) until this call has read the words -- check once per step where results are consumed."""
     code, detail = c_int(0), c_int(0)
     check(load().ksb_device_status(ctypes.byref(code), ctypes.byref(detail)), "ksb_device_status")
     return code.value, detail.value

@@ -84,9 +84,37 @@ int sm_count() {
   return cached[dev];
 }
 
+// Self-test of the bounded wait: thread 0 waits for a barrier phase that nothing completes, with a short limit, and
+// must come back with the time-out recorded; the other threads wait for it at a block barrier.  The kernel returns
+// by itself and leaves the context usable.
+constexpr int SELFTEST_KERNEL_ID = 15;
+__global__ void bounded_wait_selftest_kernel(int* status, uint64_t limit_ns, int* returned) {
+  __shared__ uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_limit(b, 0, status, (SELFTEST_KERNEL_ID << 16) | 1, limit_ns, 0x3u);
+    *returned = ok ? 1 : 2;
+  }
+  __syncthreads();
+}
+
 }  // namespace ksb
 
 extern "C" {
+
+int ksb_selftest_bounded_wait(int64_t limit_ns, int* returned, ksb_stream_t stream) {
+  if (limit_ns <= 0 || limit_ns > 1000000000ll) return ksb::fail(KSB_ERR_INVALID, "limit_ns must be in (0, 1e9]");
+  if (!returned) return ksb::fail(KSB_ERR_INVALID, "null pointer");
+  int* st = ksb::status_words();
+  if (!st) return ksb::fail(KSB_ERR_CUDA, "status words unavailable");
+  ksb::bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(st, static_cast<uint64_t>(limit_ns), returned);
+  return ksb::check_launch("bounded wait self-test");
+}
 
 int ksb_version(void) { return 100; }
 

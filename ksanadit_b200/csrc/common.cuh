@@ -80,23 +80,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #define KSB_WAIT_LIMIT_NS 2000000000ull  // 2 s: far above any legitimate wait inside these kernels
 #endif
 
-// Bounded wait.  Returns false (after recording `site`) when the limit passes or when another
-// thread of the grid has already raised an error.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int site) {
+// Bounded wait.  Returns false (after recording `site`) when `limit_ns` passes or when another
+// thread of the grid has already raised an error.  The status words are sticky: once set, every later wait of
+// every kernel on that GPU gives up at its first check until ksb_device_status() has read and cleared them.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int* status, int site, uint64_t limit_ns,
+                                                uint32_t check_mask) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0x3ff) == 0) {
+    if ((it & check_mask) == 0) {
       if (error_raised(status)) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > KSB_WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         report_error(status, KSB_ERR_WAIT_TIMEOUT, site);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int site) {
+  return mbar_wait_limit(bar, parity, status, site, KSB_WAIT_LIMIT_NS, 0x3ffu);
 }
 
 // Whole-warp bounded wait: every lane waits, and the warp proceeds only if every lane succeeded, so the

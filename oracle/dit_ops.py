@@ -190,13 +190,14 @@ def make_attn_fn(mode):
 # --------------------------------------------------------------------------- Wan block
 
 
-def wan_block_forward(p, x, e, context, grid, linear="fp8", attn="sage", eps=1e-6, sp_rank=0, sp_size=1, a2a=None):
+def wan_block_forward(p, x, e, context, grid, linear="fp8", attn="sage", eps=1e-6, sp_rank=0, sp_size=1, a2a=None, rope="default"):
     """WanAttentionBlock.forward (wan_model.py:325-393) on x [B,L,C], e [B,1,6,C], context [B,Lc,C].
 
     p: dict with 'modulation' [1,6,C]; LinearParams under 'self.q','self.k','self.v','self.o',
     'cross.q','cross.k','cross.v','cross.o','ffn.0','ffn.2'; fp32 vectors 'self.norm_q','self.norm_k',
     'cross.norm_q','cross.norm_k','norm3.w','norm3.b'; int 'num_heads'.
     a2a: optional (scatter_heads_gather_seq, scatter_seq_gather_heads) pair for Ulysses.
+    rope: "default" (complex fp64, rope.py:62-128) or "comfy" (2x2 matrices in the activation dtype, rope.py:151-212).
     """
     lin = make_linear_fn(linear)
     att = make_attn_fn(attn)
@@ -209,8 +210,13 @@ def wan_block_forward(p, x, e, context, grid, linear="fp8", attn="sage", eps=1e-
     q = rmsnorm_fp32(lin(p["self.q"], h), p["self.norm_q"], eps).view(B, L, n, d)
     k = rmsnorm_fp32(lin(p["self.k"], h), p["self.norm_k"], eps).view(B, L, n, d)
     v = lin(p["self.v"], h).view(B, L, n, d)
-    q = torch.stack([apply_wan_rope(q[b], grid, sp_rank, sp_size) for b in range(B)])
-    k = torch.stack([apply_wan_rope(k[b], grid, sp_rank, sp_size) for b in range(B)])
+    if rope == "comfy":
+        assert sp_size == 1
+        q = torch.stack([apply_comfy_rope(q[b], grid) for b in range(B)])
+        k = torch.stack([apply_comfy_rope(k[b], grid) for b in range(B)])
+    else:
+        q = torch.stack([apply_wan_rope(q[b], grid, sp_rank, sp_size) for b in range(B)])
+        k = torch.stack([apply_wan_rope(k[b], grid, sp_rank, sp_size) for b in range(B)])
     if a2a is not None:
         q, k, v = (a2a[0](t) for t in (q, k, v))
     y = att(q, k, v)

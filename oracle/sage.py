@@ -58,13 +58,22 @@ def sage_prepass(q, k, v, sm_scale=None, km=None):
     return dict(q8=q8, qs=qs, k8=k8, ks=ks, vt8=vt8, vs=vs, km=km)
 
 
-def sage_core(pp, Lq, Lk, tile_mask=None, out_dtype=torch.float32):
-    """Online-softmax INT8-QK / FP8-PV core on pre-quantised tensors -> [Lq,H,D]."""
+def sage_core(pp, Lq, Lk, tile_mask=None, out_dtype=torch.float32, q_blocks=None):
+    """Online-softmax INT8-QK / FP8-PV core on pre-quantised tensors -> [Lq,H,D].
+
+    q_blocks: optional list of 128-row Q block numbers; only those are computed and the result is
+    [len(q_blocks) * 128, H, D] (rows past Lq included) -- the sampled check of sequences too long to do whole."""
     q8, qs, k8, ks, vt8, vs = pp["q8"], pp["qs"], pp["k8"], pp["ks"], pp["vt8"], pp["vs"]
     H, Lqp, D = q8.shape
     Lkp = k8.shape[1]
     nq, nkv = Lqp // 128, Lkp // 128
     qf = q8.float().view(H, nq, 128, D)
+    if q_blocks is not None:
+        sel = torch.as_tensor(list(q_blocks), dtype=torch.long)
+        qf, qs = qf[:, sel], qs[:, sel]
+        if tile_mask is not None:
+            tile_mask = torch.as_tensor(tile_mask)[sel]
+        nq = len(sel)
     kf = k8.float()
     vf = vt8.float()  # [H, D, Lkp]
     m = torch.full((H, nq, 128), float("-inf"))
@@ -94,6 +103,8 @@ def sage_core(pp, Lq, Lk, tile_mask=None, out_dtype=torch.float32):
         m = m_new
     lsafe = torch.where(l > 0, l, torch.ones_like(l))
     out = O / lsafe[..., None] * vs[:, None, None, :]
+    if q_blocks is not None:
+        return out.reshape(H, nq * 128, D).permute(1, 0, 2).contiguous().to(out_dtype)
     out = out.view(H, Lqp, D)[:, :Lq].permute(1, 0, 2).contiguous()
     return out.to(out_dtype)
 

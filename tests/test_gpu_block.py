@@ -165,3 +165,77 @@ def test_per_head_rmsnorm_and_qwen_rope():
         d = (xd.cpu().float() - ref.float()).abs()
         assert float(d.max()) <= 2 ** -6 * float(ref.float().abs().max())
         assert cosine(xd.cpu(), ref) > 0.99999
+
+
+def test_comfy_rope_table_matches_reference_formulation(golden):
+    """rope_func="comfy" (ksana/utils/rope.py:151-212): the kernel rotates with a table of bf16-rounded cos / sin, like
+    the reference's 2x2 matrices held in the activation dtype.  The reference rounds twice per output (product, then
+    addcmul), the kernel once, so single outputs may differ by one bf16 ulp."""
+    from ksanadit_b200 import ops
+    v = golden["comfy_rope"]["bf16"]
+    x, grid, ref = v["x"], tuple(int(t) for t in v["grid"]), v["y"]
+    L, N, Dh = x.shape
+    assert torch.equal(D.apply_comfy_rope(x, grid), ref)  # the oracle restatement is the reference, bit for bit
+    xd = x.reshape(L, N * Dh).clone().cuda()
+    ones = torch.ones(N * Dh)
+    # unit RMSNorm weight on unit-RMS rows would still rescale: rotate rows that are already normalised instead
+    n = D.rmsnorm_fp32(x.reshape(L, N * Dh), ones)
+    want = D.apply_comfy_rope(n.view(L, N, Dh), grid).reshape(L, N * Dh)
+    ops.rmsnorm_rope_inplace(xd, ones.cuda(), 1e-6, ops.comfy_rope_table(Dh, 1024, dtype=torch.bfloat16), grid)
+    d = (xd.cpu().float() - want.float()).abs()
+    assert float(d.max()) <= 2 ** -7 * float(want.float().abs().max())
+    assert float((d > 0).float().mean()) < 0.25
+    dflt = D.apply_wan_rope(n.view(L, N, Dh), grid).reshape(L, N * Dh)
+    assert float((xd.cpu().float() - want.float()).abs().mean()) < float((dflt.float() - want.float()).abs().mean())
+
+
+def test_wan_block_with_comfy_rope_matches_oracle():
+    from ksanadit_b200 import _lib
+    from ksanadit_b200.wan_block import B200WanBlock
+    dim, ffn, heads, grid, ctx = 256, 768, 2, (2, 6, 8), 40
+    L = grid[0] * grid[1] * grid[2]
+    p = D.make_wan_block_params(dim, ffn, heads, seed=0)
+    x = D.make_activations(L, dim, seed=0)[None]
+    g = torch.Generator().manual_seed(0)
+    e = (torch.randn(1, 1, 6, dim, generator=g) * 0.1).to(torch.bfloat16)
+    c = torch.randn(1, ctx, dim, generator=g).to(torch.bfloat16)
+    ref = D.wan_block_forward(p, x, e, c, grid, linear="fp8", attn="sage", rope="comfy").float()
+    blk = B200WanBlock(dim, ffn, heads, device="cuda").load_block_state_dict(block_state_dict(p))
+    with torch.no_grad():
+        out = blk(x.cuda(), e.cuda(), grid_sizes=[grid], context=c.cuda(), rope_func="comfy").float().cpu()
+        with pytest.raises(_lib.KsanaB200Error):
+            blk(x.cuda(), e.cuda(), grid_sizes=[grid], context=c.cuda(), rope_func="something else")
+    _lib.assert_device_ok()
+    assert cosine(out, ref) >= BLOCK_COS and max_abs_rel(out, ref) <= BLOCK_MAR
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_qwen_block_zero_cond_t_per_token_modulation(dtype, golden):
+    """zero_cond_t blocks (qwen/transformer.py:171-188,206-208): per-token choice between two modulation rows."""
+    from ksanadit_b200 import _lib
+    from ksanadit_b200.qwen_block import B200QwenBlock
+    dim, ffn, heads, grid, Lt = 256, 1024, 2, (1, 6, 8), 10
+    p = D.make_qwen_block_params(dim, ffn, heads, seed=5, dtype=dtype)
+    for nm in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+        p[nm] = p[nm].to(dtype)
+    gz = golden["qwen_block_zero_cond"]
+    Li = grid[1] * grid[2]
+    g = torch.Generator().manual_seed(9)
+    img = D.make_activations(Li, dim, seed=6, dtype=dtype)
+    txt = torch.randn(Lt, dim, generator=g).to(dtype)
+    temb2, index = gz["temb"].to(dtype), gz["index"]
+    ia, ta = D.qwen_rope_angles(grid, Lt)
+    i_ref, t_ref = D.qwen_block_forward(p, img, txt, temb2, ia, ta, linear="fp8", attn="sage", modulate_index=index)
+    blk = B200QwenBlock(dim, heads, ffn, device="cuda", dtype=dtype, zero_cond_t=True).load_block_state_dict(_qwen_state_dict(p))
+    with torch.no_grad():
+        t_out, i_out = blk(img[None].cuda(), txt[None].cuda(), temb2.cuda(), img_grid=grid, modulate_index=index[None].cuda())
+        with pytest.raises(_lib.KsanaB200Error):
+            blk(img[None].cuda(), txt[None].cuda(), temb2.cuda(), img_grid=grid)  # a zero_cond_t block needs the index
+    _lib.assert_device_ok()
+    for out, ref in ((i_out[0].cpu().float(), i_ref.float()), (t_out[0].cpu().float(), t_ref.float())):
+        assert cosine(out, ref) >= BLOCK_COS and max_abs_rel(out, ref) <= BLOCK_MAR
+    # every token on row 0 gives a different image stream: the index really selects
+    i_all0, _ = D.qwen_block_forward(p, img, txt, temb2, ia, ta, linear="fp8", attn="sage", modulate_index=torch.zeros_like(index))
+    assert max_abs_rel(i_out[0].cpu().float(), i_all0.float()) > max_abs_rel(i_out[0].cpu().float(), i_ref.float())
+    if dtype == torch.bfloat16:  # the reference's own block output (fp32 Linear + SDPA) on the same inputs
+        assert cosine(i_out[0].cpu().float(), gz["img_y"].float()) >= BLOCK_COS
