@@ -97,8 +97,10 @@ int ksb_layernorm_quant_fp8(const void* x, int dtype, int64_t M, int64_t K, int6
  * nn.GELU(approximate="tanh") (wan_model.py:317-321) and torch.addcmul(x, y, gate) (wan_model.py:385,392).
  *   out[m,n] = epi( (sum_k a[m,k]*w[n,k])_fp32 * a_scale[m] * w_scale[n] + bias[n] )
  * a: [M,K] e4m3 contiguous; w: [N,K] e4m3 contiguous; bias: half [N] or NULL; out: [M,N] half, row
- * stride ldo.  resid: [M,N] half (row stride ldr) and gate: [gate_rows, N] half with gate_rows 1 or M,
- * both only for KSB_EPI_GATE_RESIDUAL.  K % 16 == 0, N % 8 == 0. */
+ * stride ldo.  resid: [M,N] half (row stride ldr) and gate: [gate_rows, N] half, both only for
+ * KSB_EPI_GATE_RESIDUAL.  gate_rows divides M and row m uses gate row m / (M / gate_rows): 1 = one gate for all
+ * rows, M = one per token, B = one per sample of a batch of B equal-length sequences folded into M
+ * (cond / uncond batching, ksana/generators/generator.py:356-375).  K % 16 == 0, N % 8 == 0. */
 int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, const float* w_scale, const void* bias,
                  int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo, int epilogue,
                  const void* resid, int64_t ldr, const void* gate, int64_t gate_rows, ksb_stream_t stream);

@@ -51,6 +51,7 @@ struct Params {
   int64_t ldr;
   const void* gate;
   int64_t gate_rows;
+  int rows_per_gate;  // M / gate_rows: row m reads gate row m / rows_per_gate
   int* status;
   // KSB_EPI_SCATTER_HEADS (fused QKV projection + Ulysses exchange): the output row of local token m and
   // column n = which * C + head * 128 + d goes to peer head / heads_per_peer, into its [tokens_all, 3, heads_per_peer,
@@ -202,7 +203,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       T* orow = out + static_cast<int64_t>(row) * p.ldo + tn * BN;
       const T* rrow = p.resid ? static_cast<const T*>(p.resid) + static_cast<int64_t>(row) * p.ldr + tn * BN : nullptr;
-      const T* grow = (p.gate && p.gate_rows != 1) ? static_cast<const T*>(p.gate) + static_cast<int64_t>(row) * p.N + tn * BN : nullptr;
+      const T* grow = (p.gate && p.gate_rows != 1) ? static_cast<const T*>(p.gate) + static_cast<int64_t>(row / p.rows_per_gate) * p.N + tn * BN : nullptr;
       const bool scatter = p.epilogue == KSB_EPI_SCATTER_HEADS;
       float ssq = 0.f;
       // The residual (and a per-row gate) are fetched one 32-column chunk ahead when the main loop is short
@@ -329,6 +330,7 @@ extern "C" int ksb_fp8_gemm_qkv_scatter(const void* a, const float* a_scale, con
     return fail(KSB_ERR_INVALID, "n_peers must be 1..%d, rank inside it, heads divisible by it", KSB_MAX_PEERS);
   if (!a || !a_scale || !w || !w_scale || !peer_out || !tile_sumsq) return fail(KSB_ERR_INVALID, "null pointer");
   gemm::Params p{};
+  p.rows_per_gate = 1;
   p.M = (int)M; p.N = (int)(3 * C); p.K = (int)K;
   p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = peer_out[rank]; p.ldo = 3 * C; p.epilogue = KSB_EPI_SCATTER_HEADS;
   for (int i = 0; i < n_peers; ++i) {
@@ -354,15 +356,17 @@ extern "C" int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, 
   if (epilogue == KSB_EPI_GATE_RESIDUAL) {
     if (!resid || !gate) return fail(KSB_ERR_INVALID, "gate-residual epilogue needs resid and gate");
     if (ldr < N || ldr % 8 != 0 || !aligned16(resid) || !aligned16(gate)) return fail(KSB_ERR_INVALID, "resid/gate alignment");
-    if (gate_rows != 1 && gate_rows != M) return fail(KSB_ERR_INVALID, "gate_rows must be 1 or M");
+    if (gate_rows < 1 || gate_rows > M || M % gate_rows != 0) return fail(KSB_ERR_INVALID, "gate_rows must divide M");
   } else {
     resid = nullptr;
     gate = nullptr;
   }
   gemm::Params p{};
+  p.rows_per_gate = 1;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = out; p.ldo = ldo; p.epilogue = epilogue;
   p.resid = resid; p.ldr = ldr; p.gate = gate; p.gate_rows = gate_rows;
+  p.rows_per_gate = (gate && gate_rows > 0) ? static_cast<int>(M / gate_rows) : 1;
   return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
 }
 

@@ -77,13 +77,23 @@ def pad128(n: int) -> int:
 # ----------------------------------------------------------------------------- FP8 Linear pieces
 
 
-def quant_fp8_rowwise(x: torch.Tensor):
+def _quant_out(out, M, K, device):
+    """(q [M,K] e4m3, s [M] fp32): fresh tensors, or the caller's (row slices of a larger batch buffer) after a shape check."""
+    if out is None:
+        return torch.empty(M, K, dtype=torch.float8_e4m3fn, device=device), torch.empty(M, dtype=torch.float32, device=device)
+    q, s = out
+    if q.shape != (M, K) or s.shape != (M,) or q.dtype != torch.float8_e4m3fn or s.dtype != torch.float32 or not q.is_contiguous() or not s.is_contiguous():
+        raise _lib.KsanaB200Error(f"out must be a contiguous ([{M}, {K}] float8_e4m3fn, [{M}] float32) pair")
+    _cuda(q, s)
+    return q, s
+
+
+def quant_fp8_rowwise(x: torch.Tensor, out=None):
     """x [M,K] half (row stride allowed) -> (q [M,K] float8_e4m3fn, scale [M] fp32)."""
     _cuda(x)
     assert x.dim() == 2 and x.stride(1) == 1
     M, K = x.shape
-    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
-    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    q, s = _quant_out(out, M, K, x.device)
     _lib.check(_lib.load().ksb_quant_fp8_rowwise(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(q), _p(s), _stream()),
                "ksb_quant_fp8_rowwise")
     STATS.count(1)
@@ -102,7 +112,7 @@ def quant_fp8_static(x: torch.Tensor, scale_input: torch.Tensor | None):
     return q, s
 
 
-def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False, round_product=False):
+def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False, round_product=False, out=None):
     """h = shift + LN(x)*(1+scale) -> per-token FP8.  x [M,K]; shift/scale [1,K] or [M,K].
     round_product: round LN(x)*(1+scale) to half before adding shift (the Qwen-Image block's eager order)."""
     _cuda(x, shift, scale)
@@ -110,8 +120,7 @@ def adaln_quant_fp8(x, shift, scale, eps=1e-6, want_h=False, round_product=False
     shift = shift.reshape(-1, K).contiguous()
     scale = scale.reshape(-1, K).contiguous()
     assert shift.shape == scale.shape and shift.dtype == x.dtype == scale.dtype
-    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
-    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    q, s = _quant_out(out, M, K, x.device)
     h = torch.empty(M, K, dtype=x.dtype, device=x.device) if want_h else None
     _lib.check(_lib.load().ksb_adaln_quant_fp8(_p(x), _dt(x), M, K, x.stride(0) if M > 1 else K, _p(shift), _p(scale),
                                                shift.shape[0], int(round_product), float(eps), _p(h), _p(q), _p(s), _stream()),
@@ -228,27 +237,42 @@ def sage_kmean(k):
     return km
 
 
-def sage_quant_int8(x, block, premul=0.0, mean=None):
-    """x [L,H,128] -> (int8 [H,Lpad,128], scale [H, Lpad/block])."""
+def sage_quant_int8(x, block, premul=0.0, mean=None, out=None):
+    """x [L,H,128] -> (int8 [H,Lpad,128], scale [H, Lpad/block]).  out: that pair, preallocated (e.g. the head slots of
+    one sample inside the operands of a batched attention launch)."""
     _cuda(x, mean)
     L, H, D, ts, hs = _lhd(x)
     Lp = pad128(L)
-    out = torch.empty(H, Lp, D, dtype=torch.int8, device=x.device)
-    sc = torch.empty(H, Lp // block, dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(H, Lp, D, dtype=torch.int8, device=x.device)
+        sc = torch.empty(H, Lp // block, dtype=torch.float32, device=x.device)
+    else:
+        out, sc = out
+        if out.shape != (H, Lp, D) or sc.shape != (H, Lp // block) or out.dtype != torch.int8 or sc.dtype != torch.float32 \
+                or not out.is_contiguous() or not sc.is_contiguous():
+            raise _lib.KsanaB200Error(f"out must be a contiguous ([{H}, {Lp}, {D}] int8, [{H}, {Lp // block}] float32) pair")
+        _cuda(out, sc)
     _lib.check(_lib.load().ksb_sage_quant_int8(_p(x), _dt(x), L, H, D, ts, hs, block, float(premul), _p(mean), _p(out), _p(sc),
                                                _stream()), "ksb_sage_quant_int8")
     STATS.count(1)
     return out, sc
 
 
-def sage_quant_v(v):
-    """v [L,H,128] -> (vt [H,128,Lpad] float8_e4m3fn, vs [H,128])."""
+def sage_quant_v(v, out=None):
+    """v [L,H,128] -> (vt [H,128,Lpad] float8_e4m3fn, vs [H,128]).  out: that pair, preallocated."""
     _cuda(v)
     L, H, D, ts, hs = _lhd(v)
     Lp = pad128(L)
     amax = torch.empty(H * D, dtype=torch.float32, device=v.device)
-    vt = torch.empty(H, D, Lp, dtype=torch.float8_e4m3fn, device=v.device)
-    vs = torch.empty(H, D, dtype=torch.float32, device=v.device)
+    if out is None:
+        vt = torch.empty(H, D, Lp, dtype=torch.float8_e4m3fn, device=v.device)
+        vs = torch.empty(H, D, dtype=torch.float32, device=v.device)
+    else:
+        vt, vs = out
+        if vt.shape != (H, D, Lp) or vs.shape != (H, D) or vt.dtype != torch.float8_e4m3fn or vs.dtype != torch.float32 \
+                or not vt.is_contiguous() or not vs.is_contiguous():
+            raise _lib.KsanaB200Error(f"out must be a contiguous ([{H}, {D}, {Lp}] float8_e4m3fn, [{H}, {D}] float32) pair")
+        _cuda(vt, vs)
     _lib.check(_lib.load().ksb_sage_quant_v_fp8(_p(v), _dt(v), L, H, D, ts, hs, _p(amax), _p(vt), _p(vs), _stream()),
                "ksb_sage_quant_v_fp8")
     STATS.count(2)

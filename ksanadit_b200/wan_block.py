@@ -119,13 +119,19 @@ class B200WanBlock(torch.nn.Module):
         return self
 
     # ------------------------------------------------------------------ pieces
-    def _context_kv(self, context):
-        """Quantised cross-attention K / V of the text context.  They depend only on the block's weights and
-        the prompt; with ``cache_context`` they are kept across denoise steps while the same context tensor is
-        passed (the reference recomputes them every step, wan_model.py:237-238, and so does the default here)."""
-        key = (context.data_ptr(), context._version, tuple(context.shape))
-        if self.cache_context and self._ctx_cache is not None and self._ctx_cache[0] == key:
-            return self._ctx_cache[1]
+    def _context_kv(self, context, owner=None, slot=0):
+        """Quantised cross-attention K / V of the text context [Lc, C].  They depend only on the block's weights and
+        the prompt; with ``cache_context`` they are kept across denoise steps (the reference recomputes them every
+        step, wan_model.py:237-238, and so does the default here).  A cached entry is reused only while the caller
+        passes the very same tensor object ``owner`` (the batch the row ``slot`` was taken from), unmodified: the
+        cache holds a reference to it, so a new prompt tensor can never be mistaken for the old one by its address.
+        One entry per batch row."""
+        if self.cache_context and owner is not None:
+            if self._ctx_cache is None:
+                self._ctx_cache = {}
+            hit = self._ctx_cache.get(slot)
+            if hit is not None and hit[0] is owner and hit[1] == owner._version:
+                return hit[2]
         ca = self.cross_attn
         Lc = context.shape[0]
         k = ca.k(context)
@@ -136,7 +142,8 @@ class B200WanBlock(torch.nn.Module):
         k8, ks = ops.sage_quant_int8(k3, ops.K_BLOCK, mean=km)
         vt, vs = ops.sage_quant_v(v3)
         val = (k8, ks, vt, vs, Lc)
-        self._ctx_cache = (key, val)
+        if self.cache_context and owner is not None:
+            self._ctx_cache[slot] = (owner, owner._version, val)
         return val
 
     # The sequence-parallel self-attention with the exchange fused into the kernels' output stages, in three
@@ -203,7 +210,7 @@ class B200WanBlock(torch.nn.Module):
             o = distribute.sequence_to_heads(o)  # [L, H, D]
         return o.reshape(L, C)
 
-    def _block_one(self, x, e6, context, grid, rope):
+    def _block_one(self, x, e6, context, grid, rope, ctx_owner=None, slot=0):
         """x [L, C]; e6 six [1, C] or [L, C] tensors (modulation already added); context [Lc, C]."""
         L, C = x.shape
         if self._ones is None or self._ones.device != x.device:
@@ -221,7 +228,7 @@ class B200WanBlock(torch.nn.Module):
             hq, hs = ops.quant_fp8_rowwise(x)
         q = ca.q.forward_quantized(hq, hs, self.dtype)
         ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
-        k8, ks, vt, vs, Lc = self._context_kv(context)
+        k8, ks, vt, vs, Lc = self._context_kv(context, ctx_owner, slot)
         q8, qs = ops.sage_quant_int8(q.view(L, self.num_heads, HEAD), ops.Q_BLOCK, premul=ops.q_premul(HEAD))
         o = ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, Lc, self.dtype).view(L, C)
         oq, os_ = ops.quant_fp8_rowwise(o)
@@ -232,6 +239,90 @@ class B200WanBlock(torch.nn.Module):
         hq, hs = ops.quant_fp8_rowwise(h)
         x = self.ffn[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=e6[5], out=x)
         return x
+
+    def _per_sample_quant(self, B, L, K, fn):
+        """Runs a row-wise quantiser once per sample, each writing its rows of one [B*L, K] activation buffer."""
+        dev = self.modulation.device
+        q = torch.empty(B * L, K, dtype=torch.float8_e4m3fn, device=dev)
+        s = torch.empty(B * L, dtype=torch.float32, device=dev)
+        for b in range(B):
+            fn(b, (q[b * L:(b + 1) * L], s[b * L:(b + 1) * L]))
+        return q, s
+
+    def _block_batched(self, x, em, context, grid, rope):
+        """The block on a batch of B equal-length sequences folded into the row dimension (cond / uncond batching,
+        ksana/generators/generator.py:356-375,859-871): every Linear runs once at M = B * L, so its weights are streamed
+        once and its tail is paid once; every attention runs once over B * H heads.  x [B, L, C]; em [B, 1, 6, C]
+        (modulation per sample; the row-wise passes that take a modulation vector run once per sample on that sample's
+        rows of the shared buffers, the GEMM epilogues take one gate row per sample); context [B, Lc, C]."""
+        B, L, C = x.shape
+        H, M = self.num_heads, B * L
+        dev = x.device
+        if self._ones is None or self._ones.device != dev:
+            self._ones = torch.ones(1, C, dtype=self.dtype, device=dev)
+        e6 = [em[:, 0, i].contiguous() for i in range(6)]  # six [B, C]
+        x2 = x.reshape(M, C)
+        sa, ca = self.self_attn, self.cross_attn
+        Lp = ops.pad128(L)
+
+        def heads_operands(Lk_pad):
+            return (torch.empty(B * H, Lk_pad, HEAD, dtype=torch.int8, device=dev),
+                    torch.empty(B * H, Lk_pad // ops.K_BLOCK, dtype=torch.float32, device=dev),
+                    torch.empty(B * H, HEAD, Lk_pad, dtype=torch.float8_e4m3fn, device=dev),
+                    torch.empty(B * H, HEAD, dtype=torch.float32, device=dev))
+
+        def quant_q(q2):  # [M, C] -> INT8 Q of B * H heads
+            q8 = torch.empty(B * H, Lp, HEAD, dtype=torch.int8, device=dev)
+            qs = torch.empty(B * H, Lp // ops.Q_BLOCK, dtype=torch.float32, device=dev)
+            for b in range(B):
+                ops.sage_quant_int8(q2[b * L:(b + 1) * L].view(L, H, HEAD), ops.Q_BLOCK, premul=ops.q_premul(HEAD),
+                                    out=(q8[b * H:(b + 1) * H], qs[b * H:(b + 1) * H]))
+            return q8, qs
+
+        def requant_attention_output(o):  # o [L, B, H, 128]: sample b's rows are a strided [L, C] view
+            return self._per_sample_quant(B, L, C, lambda b, out: ops.quant_fp8_rowwise(o[:, b].reshape(L, C), out=out))
+
+        # ---- self-attention
+        xq, sx = self._per_sample_quant(B, L, C, lambda b, out: ops.adaln_quant_fp8(x[b], e6[0][b:b + 1], e6[1][b:b + 1], self.eps, out=out))
+        qkv = sa.qkv.forward_quantized(xq, sx, self.dtype)  # [M, 3C]
+        k8, ks, vt, vs = heads_operands(Lp)
+        for b in range(B):
+            rows = qkv[b * L:(b + 1) * L]
+            km = ops.rmsnorm_rope_inplace(rows[:, C:2 * C], sa.norm_k.weight, self.eps, rope, grid, want_mean=True)
+            ops.rmsnorm_rope_inplace(rows[:, :C], sa.norm_q.weight, self.eps, rope, grid)
+            t = rows.view(L, 3, H, HEAD)
+            ops.sage_quant_int8(t[:, 1], ops.K_BLOCK, mean=km.view(H, HEAD), out=(k8[b * H:(b + 1) * H], ks[b * H:(b + 1) * H]))
+            ops.sage_quant_v(t[:, 2], out=(vt[b * H:(b + 1) * H], vs[b * H:(b + 1) * H]))
+        q8, qs = quant_q(qkv[:, :C])
+        offs, ents, order = self.tile_lists if self.tile_lists is not None else (None, None, None)
+        o = torch.empty(L, B, H, HEAD, dtype=self.dtype, device=dev)
+        ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, self.dtype, offs, ents, out=o.view(L, B * H, HEAD), tile_order=order)
+        aq, sq = requant_attention_output(o)
+        x2 = sa.o.forward_quantized(aq, sq, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x2, gate=e6[2])
+        # ---- cross-attention
+        if self.cross_attn_norm:
+            hq, hs = ops.layernorm_quant_fp8(x2, self.norm3.weight, self.norm3.bias, self.eps)
+        else:
+            hq, hs = ops.quant_fp8_rowwise(x2)
+        q = ca.q.forward_quantized(hq, hs, self.dtype)
+        ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
+        Lc = context.shape[1]
+        ck8, cks, cvt, cvs = heads_operands(ops.pad128(Lc))
+        for b in range(B):
+            kb, sb, vb, vsb, _ = self._context_kv(context[b], context, b)
+            for dst, src in ((ck8, kb), (cks, sb), (cvt, vb), (cvs, vsb)):
+                dst[b * H:(b + 1) * H].copy_(src)
+        q8, qs = quant_q(q)
+        ops.sage_attn_core(q8, qs, ck8, cks, cvt, cvs, L, Lc, self.dtype, out=o.view(L, B * H, HEAD))
+        oq, os_ = requant_attention_output(o)
+        x2 = ca.o.forward_quantized(oq, os_, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x2, gate=self._ones, out=x2)
+        # ---- FFN
+        xq, sx = self._per_sample_quant(B, L, C, lambda b, out: ops.adaln_quant_fp8(x2[b * L:(b + 1) * L], e6[3][b:b + 1], e6[4][b:b + 1],
+                                                                                   self.eps, out=out))
+        h = self.ffn[0].forward_quantized(xq, sx, self.dtype, _lib.EPI_GELU_TANH)
+        hq, hs = ops.quant_fp8_rowwise(h)
+        x2 = self.ffn[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x2, gate=e6[5], out=x2)
+        return x2.view(B, L, C)
 
     # ------------------------------------------------------------------ WanAttentionBlock.forward signature
     def forward(self, x, e, seq_lens=None, grid_sizes=None, freqs=None, context=None, context_lens=None, step_iter=None,
@@ -251,11 +342,16 @@ class B200WanBlock(torch.nn.Module):
             raise _lib.KsanaB200Error(f"unknown rope_func {rope_func!r} (default or comfy)")
         em = (self.modulation.unsqueeze(0) + e) if e.dim() == 4 else (self.modulation + e).unsqueeze(1)  # [B, 1|L, 6, C]
         em = em.to(self.dtype)
+        grids = [tuple(int(v) for v in (grid_sizes[b].tolist() if torch.is_tensor(grid_sizes) else grid_sizes[b])) for b in range(len(grid_sizes))]
+        if len(grids) == 1 and B > 1:
+            grids = grids * B
+        if (B > 1 and em.shape[1] == 1 and all(g == grids[0] for g in grids) and self.peer_exchange is None
+                and distribute.get_world_size() == 1):
+            return self._block_batched(x, em, context, grids[0], rope)
         outs = []
-        for b in range(B):
+        for b in range(B):  # sequence-parallel runs, per-token modulation and mixed grids: one sample at a time
             e6 = [em[b, :, i].contiguous() for i in range(6)]
-            grid = tuple(int(v) for v in (grid_sizes[b].tolist() if torch.is_tensor(grid_sizes) else grid_sizes[b]))
-            outs.append(self._block_one(x[b], e6, context[b], grid, rope))
+            outs.append(self._block_one(x[b], e6, context[b], grids[b], rope, context, b))
         return torch.stack(outs) if B > 1 else outs[0].unsqueeze(0)
 
 

@@ -239,3 +239,53 @@ def test_qwen_block_zero_cond_t_per_token_modulation(dtype, golden):
     assert max_abs_rel(i_out[0].cpu().float(), i_all0.float()) > max_abs_rel(i_out[0].cpu().float(), i_ref.float())
     if dtype == torch.bfloat16:  # the reference's own block output (fp32 Linear + SDPA) on the same inputs
         assert cosine(i_out[0].cpu().float(), gz["img_y"].float()) >= BLOCK_COS
+
+
+def test_wan_block_cfg_batch_folds_into_rows():
+    """Two samples (cond / uncond: own modulation and own text context, same grid) folded into the row dimension give what
+    the two samples give one at a time -- every element is computed by the same arithmetic, only the launches differ --
+    and both match the oracle (generator.py:356-375: the reference concatenates cond and uncond on the batch axis)."""
+    from ksanadit_b200 import _lib, ops
+    from ksanadit_b200.wan_block import B200WanBlock
+    dim, ffn, heads, grid, ctx = 256, 768, 2, (2, 6, 9), 40
+    L = grid[0] * grid[1] * grid[2]  # 108 tokens: a ragged last tile inside every sample
+    p = D.make_wan_block_params(dim, ffn, heads, seed=0)
+    g = torch.Generator().manual_seed(1)
+    x = torch.stack([D.make_activations(L, dim, seed=s) for s in (3, 4)])
+    e = (torch.randn(2, 1, 6, dim, generator=g) * 0.1).to(torch.bfloat16)
+    c = torch.randn(2, ctx, dim, generator=g).to(torch.bfloat16)
+    blk = B200WanBlock(dim, ffn, heads, device="cuda").load_block_state_dict(block_state_dict(p))
+    with torch.no_grad():
+        launches0 = ops.STATS.kernels
+        both = blk(x.cuda(), e.cuda(), grid_sizes=[grid, grid], context=c.cuda())
+        n_batched = ops.STATS.kernels - launches0
+        single = [blk(x[b:b + 1].cuda(), e[b:b + 1].cuda(), grid_sizes=[grid], context=c[b:b + 1].cuda()) for b in range(2)]
+        n_single = ops.STATS.kernels - launches0 - n_batched
+    _lib.assert_device_ok()
+    assert both.shape == (2, L, dim)
+    for b in range(2):
+        assert torch.equal(both[b], single[b][0]), f"sample {b}: batched and one-at-a-time results differ"
+        ref = D.wan_block_forward(p, x[b:b + 1], e[b:b + 1], c[b:b + 1], grid, linear="fp8", attn="sage").float()
+        assert cosine(both[b].cpu().float(), ref[0]) >= BLOCK_COS and max_abs_rel(both[b].cpu().float(), ref[0]) <= BLOCK_MAR
+    assert n_batched < n_single  # one GEMM and one attention launch per stage for both samples
+
+
+def test_context_cache_is_keyed_on_the_tensor_object():
+    from ksanadit_b200.wan_block import B200WanBlock
+    dim, ffn, heads, grid = 256, 768, 2, (1, 6, 8)
+    L = 48
+    blk = B200WanBlock(dim, ffn, heads, device="cuda", cache_context=True).random_init(3)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(1, L, dim, generator=g).to(torch.bfloat16).cuda()
+    e = (torch.randn(1, 1, 6, dim, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    c1 = torch.randn(1, 24, dim, generator=g).to(torch.bfloat16).cuda()
+    with torch.no_grad():
+        y1 = blk(x, e, grid_sizes=[grid], context=c1)
+        assert torch.equal(blk(x, e, grid_sizes=[grid], context=c1), y1)  # second call takes the cached K / V
+        c2 = torch.randn(1, 24, dim, generator=g).to(torch.bfloat16).cuda()
+        addr = c1.data_ptr()
+        c1.copy_(c2)  # same storage, new prompt: the version counter moves and the entry is not reused
+        assert c1.data_ptr() == addr
+        y2 = blk(x, e, grid_sizes=[grid], context=c1)
+        fresh = B200WanBlock(dim, ffn, heads, device="cuda").random_init(3)(x, e, grid_sizes=[grid], context=c2)
+    assert torch.equal(y2, fresh) and not torch.equal(y2, y1)
