@@ -132,6 +132,17 @@ int ksb_rowsumsq_to_rstd_scatter(const float* tile_sumsq, int64_t M, int64_t C, 
 int ksb_gate_residual(const void* x, const void* y, const void* gate, int64_t gate_rows, void* out, int dtype,
                       int64_t M, int64_t N, ksb_stream_t stream);
 
+/* Residual statistics of the block-level step cache (DBCache): the residual of a group of blocks and its L1
+ * distance to the residual kept from an earlier step, in one pass over the activations.
+ * Replaces `f_n_residual = x - x_ori` (ksana/cache/dbcache.py:301-306) and the three full-tensor reductions of
+ * `compute_diff_and_decide` (dbcache.py:228-239: mean |cur - prev|, mean |cur|, mean |prev|).
+ *   r = round(x_new - x_old) in the activation dtype; sums[0] = sum round(|r - prev|), sums[1] = sum |r|,
+ *   sums[2] = sum |prev| (fp32; the caller divides by n and forms the relative difference).
+ * x_new, x_old: n half elements, n % 8 == 0; prev_residual: n elements or NULL (then sums[0] = sums[2] = 0);
+ * residual_out: receives r, or NULL; sums: 3 floats, cleared by this call on `stream`. */
+int ksb_residual_diff(const void* x_new, const void* x_old, const void* prev_residual, void* residual_out, float* sums,
+                      int dtype, int64_t n, ksb_stream_t stream);
+
 /* Sage pre-passes.  The reference reaches them through the un-vendored `sageattention` /
  * `spas_sage_attn` packages (call sites ksana/operations/attention/backends/sage_attn.py:75-81 and
  * sage_sla.py:198-228, which shows the pre-pass API: k.mean(-2), per-block INT8 Q/K with fp32 scales,

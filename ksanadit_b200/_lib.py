@@ -31,6 +31,7 @@ SIGNATURES = {
     "ksb_fp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int,
                              c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "ksb_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p]),
+    "ksb_residual_diff": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "ksb_sage_kmean_scratch_floats": (c_int64, [c_int64, c_int64, c_int64]),
     "ksb_sage_kmean": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ksb_rmsnorm_rope_scratch_floats": (c_int64, [c_int64, c_int64]),

@@ -217,6 +217,20 @@ def gate_residual(x, y, gate):
     return out
 
 
+def residual_diff(x_new, x_old, prev=None, want_residual=True):
+    """r = x_new - x_old (rounded to the activation dtype) and the fp32 sums [sum |r - prev|, sum |r|, sum |prev|]
+    (a device tensor of 3 floats) in one pass -- the reductions the block-level step cache decides on."""
+    _cuda(x_new, x_old, prev)
+    assert x_new.shape == x_old.shape and x_new.dtype == x_old.dtype and x_new.is_contiguous() and x_old.is_contiguous()
+    assert prev is None or (prev.shape == x_new.shape and prev.dtype == x_new.dtype and prev.is_contiguous())
+    res = torch.empty_like(x_new) if want_residual else None
+    sums = torch.empty(3, dtype=torch.float32, device=x_new.device)
+    _lib.check(_lib.load().ksb_residual_diff(_p(x_new), _p(x_old), _p(prev), _p(res), _p(sums), _dt(x_new), x_new.numel(), _stream()),
+               "ksb_residual_diff")
+    STATS.count(1)
+    return res, sums
+
+
 # ----------------------------------------------------------------------------- Sage attention pieces
 
 

@@ -357,16 +357,18 @@ class B200WanBlock(torch.nn.Module):
 
 class B200WanDenoiseStep(torch.nn.Module):
     """The per-step hot loop of WanModel: ``for block in self.blocks: x = block(x, ...)`` (wan_model.py:785-793)
-    over a token shard, for a Wan-shaped stack of blocks."""
+    over a token shard, for a Wan-shaped stack of blocks.  With a ``step_cache`` (``step_cache.B200DBCache``) the loop
+    runs through the cache, which may skip all but the first blocks of a step (ksana/cache/dbcache.py:287-344)."""
 
     def __init__(self, num_layers, dim, ffn_dim, num_heads, device="cuda", dtype=torch.bfloat16, tile_lists=None, seed=0,
-                 cache_context=False):
+                 cache_context=False, step_cache=None):
         super().__init__()
         self.blocks = torch.nn.ModuleList(
             [B200WanBlock(dim, ffn_dim, num_heads, block_id=i, device=device, dtype=dtype, tile_lists=tile_lists,
                           cache_context=cache_context).random_init(seed + i)
              for i in range(num_layers)]
         )
+        self.step_cache = step_cache
 
     def use_peer_exchange(self, ex):
         """Route every block's Ulysses exchange through ``ex`` (distribute.PeerExchange; None = NCCL all-to-alls)."""
@@ -374,7 +376,9 @@ class B200WanDenoiseStep(torch.nn.Module):
             blk.peer_exchange = ex
         return self
 
-    def forward(self, x, e, grid_sizes, context):
+    def forward(self, x, e, grid_sizes, context, phase="cond", step_iter=0, timestep=0):
+        if self.step_cache is not None:
+            return self.step_cache(phase, x, step_iter, timestep, list(self.blocks), e=e, grid_sizes=grid_sizes, context=context)
         for blk in self.blocks:
             x = blk(x, e, grid_sizes=grid_sizes, context=context)
         return x

@@ -315,6 +315,46 @@ def main():
     assert float((iz_ref != i_all0).float().mean()) > 0.2, "the index must change the image stream"
     gold["qwen_block_zero_cond"] = dict(temb=temb2, index=index[0], img_y=iz_ref[0], txt_y=tz_ref[0])
 
+    # ---- (9) block-level step cache (cache/dbcache.py:60-450) on a toy block stack ----------
+    from ksana.cache.dbcache import DBCache
+    from ksana.config.cache_config.dbcache import DBCacheConfig as RefDBCfg
+    from ksana.models.model_key import KsanaModelKey
+
+    from ksanadit_b200.step_cache import B200DBCache, DBCacheConfig
+
+    def eager_diff(x_new, x_old, prev):
+        r = x_new - x_old
+        if prev is None or prev.shape != r.shape:
+            return r, None
+        cm, pm = torch.abs(r).mean() + 1e-8, torch.abs(prev).mean() + 1e-8
+        return r, float(torch.abs(r - prev).mean() / ((cm + pm) / 2))
+
+    nb = 6
+    gw = torch.Generator().manual_seed(21)
+    toy_w = [torch.randn(32, 32, generator=gw) * 0.05 for _ in range(nb)]
+    toy_blocks = [(lambda x, scale=1.0, w=w: x + torch.tanh(x.float() @ w).to(x.dtype) * scale) for w in toy_w]
+    x_toy = torch.randn(16, 32, generator=gw).to(torch.bfloat16)
+    dbc = {"weights": torch.stack(toy_w), "x": x_toy, "cases": []}
+    for (fn, bn, thr, tay) in [(2, 1, 0.3, False), (1, 0, 0.08, False), (1, 0, 0.5, True), (0, 2, 0.2, False)]:
+        kw = dict(fn_compute_blocks=fn, bn_compute_blocks=bn, residual_diff_threshold=thr, max_warmup_steps=2, warmup_interval=1,
+                  max_cached_steps=5, max_continuous_cached_steps=2, num_blocks=nb, enable_taylorseer=tay)
+        ref_c = DBCache(KsanaModelKey.Wan2_2_T2V_14B, RefDBCfg(**kw))
+        own_c = B200DBCache(DBCacheConfig(**kw), diff_fn=eager_diff)
+        outs = []
+        for step in range(14):
+            for phase in ("cond", "uncond"):
+                xin = (x_toy * (1 + 0.02 * step) + (0.3 if phase == "uncond" else 0)).to(torch.bfloat16)
+                a = ref_c(phase, xin.clone(), step, 1000 - step * 10, toy_blocks, scale=1.0 + 0.001 * step)
+                b = own_c(phase, xin.clone(), step, 1000 - step * 10, toy_blocks, scale=1.0 + 0.001 * step)
+                assert torch.equal(a, b), (fn, bn, thr, tay, step, phase)
+                outs.append(a)
+        rs = ref_c.get_stats_summary()
+        assert rs["cond_cached_steps"] == own_c.get_stats_summary()["cond_cached_steps"] and rs["cond_cached_steps"] > 0
+        dbc["cases"].append(dict(cfg=kw, outs=torch.stack(outs), cond_cached=rs["cond_cached_steps"], uncond_cached=rs["uncond_cached_steps"],
+                                 diffs=torch.tensor(ref_c._diff_history)))
+    print("[9] DBCache on a toy block stack: product state machine == reference (outputs bit-equal, same hits; 4 settings)")
+    gold["dbcache"] = dbc
+
     out = os.path.join(HERE, "reference_vectors.pt")
     torch.save(gold, out)
     print("wrote", out, os.path.getsize(out), "bytes")
