@@ -10,7 +10,10 @@ Hooks (all are module-level names KsanaDiT looks up at call time):
   defers to KsanaDiT's own function otherwise;
 * QKV fusion switch: ``should_use_qkv_fusion`` is looked up as a global of
   ksana/operations/fuse_qkv/fuse_qkv.py at :209 -> replaced; ``remap_qkv_weights`` gains scale handling;
-* collectives: ``all_to_all`` as imported by the model modules (wan_model.py:13, qwen/attention.py:27-28).
+* collectives: ``all_to_all`` as imported by the model modules (wan_model.py:13, qwen/attention.py:27-28);
+* with ``fused_blocks=True`` also ``WanAttentionBlock.forward`` (wan_model.py:325-393): blocks built from the
+  operators above run as the fused kernel sequence on their own parameters (``adopt.py``), so the adaLN / RMSNorm /
+  RoPE / GELU / gated-residual passes between the operator calls are fused too; other blocks keep their forward.
 
 ``uninstall()`` restores everything.
 """
@@ -31,7 +34,7 @@ def _ksana(name):
         raise RuntimeError(f"KsanaDiT module {name} is not importable: {exc}") from exc
 
 
-def install(patch_collectives: bool = True) -> None:
+def install(patch_collectives: bool = True, fused_blocks: bool = False) -> None:
     if _saved:
         return
     base = _ksana("ksana.operations.attention.backends.base")
@@ -75,6 +78,13 @@ def install(patch_collectives: bool = True) -> None:
             m.all_to_all = distribute.all_to_all
         _saved["a2a"] = mods
 
+    if fused_blocks:
+        from . import adopt
+        wm = _ksana("ksana.models.wan.wan_model")
+        original = wm.WanAttentionBlock.forward
+        _saved["wan_forward"] = (wm.WanAttentionBlock, original)
+        wm.WanAttentionBlock.forward = adopt.make_fused_wan_forward(original)
+
 
 def uninstall() -> None:
     if not _saved:
@@ -88,4 +98,7 @@ def uninstall() -> None:
     fq.should_use_qkv_fusion, fq.remap_qkv_weights = a, b
     for m, fn in _saved.get("a2a", []):
         m.all_to_all = fn
+    if "wan_forward" in _saved:
+        cls, fn = _saved["wan_forward"]
+        cls.forward = fn
     _saved.clear()

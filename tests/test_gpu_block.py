@@ -289,3 +289,81 @@ def test_context_cache_is_keyed_on_the_tensor_object():
         y2 = blk(x, e, grid_sizes=[grid], context=c1)
         fresh = B200WanBlock(dim, ffn, heads, device="cuda").random_init(3)(x, e, grid_sizes=[grid], context=c2)
     assert torch.equal(y2, fresh) and not torch.equal(y2, y1)
+
+
+class _RefShapedWanBlock(torch.nn.Module):
+    """A module with the attribute layout of KsanaDiT's WanAttentionBlock built from the B200 operators (wan_model.py:
+    61-133,254-323): what `install(fused_blocks=True)` meets inside a loaded model.  Its forward is never used."""
+
+    def __init__(self, dim, ffn, heads, attention_config):
+        super().__init__()
+        from ksanadit_b200.linear import B200Fp8Linear
+
+        def rms():
+            m = torch.nn.Module()
+            m.weight = torch.nn.Parameter(torch.ones(dim, dtype=torch.float32), requires_grad=False)
+            return m
+
+        def attn(separate):
+            a = torch.nn.Module()
+            if separate:
+                a.q, a.k, a.v = (B200Fp8Linear(dim, dim) for _ in range(3))
+            else:
+                a.qkv = B200Fp8Linear(dim, 3 * dim)
+            a.o, a.norm_q, a.norm_k = B200Fp8Linear(dim, dim), rms(), rms()
+            a.attention = torch.nn.Module()
+            a.attention.attention_config = attention_config
+            return a
+
+        self.dim, self.ffn_dim, self.num_heads, self.block_id, self.eps, self.cross_attn_norm = dim, ffn, heads, 2, 1e-6, True
+        self.self_attn, self.cross_attn = attn(False), attn(True)
+        self.norm3 = torch.nn.LayerNorm(dim, 1e-6, elementwise_affine=True, dtype=torch.float32)
+        self.ffn = torch.nn.Sequential(B200Fp8Linear(dim, ffn), torch.nn.GELU(approximate="tanh"), B200Fp8Linear(ffn, dim))
+        self.modulation = torch.nn.Parameter(torch.zeros(1, 6, dim, dtype=torch.bfloat16), requires_grad=False)
+
+
+@pytest.mark.parametrize("radial", [False, True])
+def test_fused_forward_on_an_adopted_reference_shaped_block(radial):
+    """The fused sequence running on a reference-shaped module's own parameters gives what B200WanBlock gives with the same
+    weights, for the Sage backend and for the radial one (dense in early steps, tile lists afterwards)."""
+    from ksanadit_b200 import _lib, adopt
+    from ksanadit_b200.config import KsanaAttentionBackend, KsanaAttentionConfig, KsanaRadialSageAttentionConfig
+    from ksanadit_b200.wan_block import B200WanBlock
+    dim, ffn, heads = 256, 768, 2
+    frames, lh, lw = 9, 16, 32
+    grid = (frames, lh // 2, lw // 2)
+    L = grid[0] * grid[1] * grid[2]  # 1152 tokens
+    cfg = KsanaRadialSageAttentionConfig(dense_blocks_num=1, dense_attn_steps=2, decay_factor=0.2, block_size=128) if radial \
+        else KsanaAttentionConfig(backend=KsanaAttentionBackend.SAGE_ATTN)
+    ours = B200WanBlock(dim, ffn, heads, block_id=2, device="cuda").random_init(11)
+    ref_like = _RefShapedWanBlock(dim, ffn, heads, cfg).cuda()
+    sd = {k: v for k, v in ours.state_dict().items()}
+    missing, unexpected = ref_like.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    for a, b in ((ref_like.self_attn.qkv, ours.self_attn.qkv), (ref_like.ffn[0], ours.ffn[0])):
+        assert torch.equal(a.weight.view(torch.uint8), b.weight.view(torch.uint8)) and torch.equal(a.scale_weight, b.scale_weight)
+    assert adopt.why_not_adoptable(ref_like) is None
+    fused = adopt.make_fused_wan_forward(lambda *a, **k: (_ for _ in ()).throw(AssertionError("the original forward must not run")))
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(1, L, dim, generator=g).to(torch.bfloat16).cuda()
+    e = (torch.randn(1, 1, 6, dim, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    c = torch.randn(1, 40, dim, generator=g).to(torch.bfloat16).cuda()
+    kw = dict(seq_lens=torch.tensor([L]), grid_sizes=torch.tensor([grid]), freqs=None, context=c, context_lens=None,
+              latent_shape=[1, 16, frames, lh, lw])
+    with torch.no_grad():
+        dense = ours(x, e, grid_sizes=[grid], context=c)
+        early = fused(ref_like, x, e, step_iter=0, **kw)
+        late = fused(ref_like, x, e, step_iter=5, **kw)
+    _lib.assert_device_ok()
+    assert torch.equal(early, dense)
+    if not radial:
+        assert torch.equal(late, dense)
+    else:
+        impl = adopt.adopt(ref_like)._radial
+        ours.tile_lists = impl.tile_lists_for(L, L, frames, x.device)
+        with torch.no_grad():
+            sparse = ours(x, e, grid_sizes=[grid], context=c)
+        assert torch.equal(late, sparse) and not torch.equal(late, dense)
+    # a call the fused path does not take goes to the original forward
+    with pytest.raises(AssertionError, match="original forward"):
+        fused(ref_like, x, e, step_iter=0, feta_enabled=True, **kw)

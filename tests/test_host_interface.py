@@ -229,3 +229,63 @@ def test_torch_library_ops_have_shape_inference():
     with pytest.raises(Exception):
         torch.ops.ksana_b200.sage_attention(torch.zeros(8, 1, 128, dtype=torch.bfloat16), torch.zeros(8, 1, 128, dtype=torch.bfloat16),
                                             torch.zeros(8, 1, 128, dtype=torch.bfloat16))
+
+
+def test_install_fused_blocks_adopts_the_reference_block():
+    """Runs only where the KsanaDiT tree is importable: a WanAttentionBlock built from the installed operators is taken
+    over by the fused sequence on its own parameters, its state dict is untouched, and uninstall restores the forward."""
+    ref = os.environ.get("KSANA_REFERENCE", "/root/reference")
+    if not os.path.isdir(os.path.join(ref, "ksana")):
+        pytest.skip("KsanaDiT source tree not present")
+    code = f"""
+import sys
+sys.path.insert(0, {ROOT!r}); sys.path.insert(0, {os.path.join(ROOT, 'tests', 'golden')!r})
+import make_golden; make_golden.install_stubs()
+import torch, ksana
+from ksana.config import KsanaAttentionBackend, KsanaAttentionConfig
+from ksanadit_b200 import install, adopt, linear
+install.install(fused_blocks=True)
+from ksana.models.wan.wan_model import WanAttentionBlock
+from ksana.operations.ops import LayerNorm, Ops, RMSNorm
+from ksana.operations.linear.linear import Linear
+from ksana.operations.attention.pick_attn import pick_attn_op
+def build(lin, backend):
+    ops = Ops()
+    for n, c in (("Linear", lin), ("LayerNorm", LayerNorm), ("RMSNorm", RMSNorm)):
+        ops.register(n, c)
+    ops.register("Attn", pick_attn_op(KsanaAttentionConfig(backend=backend)))
+    st = {{"operations": ops, "device": "cpu", "dtype": torch.bfloat16, "rms_dtype": None}}
+    return WanAttentionBlock(256, 512, 2, block_id=3, qk_norm=True, cross_attn_norm=True, eps=1e-6, operation_settings=st)
+blk = build(linear.b200_fp8_ops(scale_input=False), KsanaAttentionBackend.SAGE_ATTN)
+keys = sorted(blk.state_dict())
+assert adopt.why_not_adoptable(blk) is None
+ab = adopt.adopt(blk)
+assert ab is adopt.adopt(blk) and ab.block_id == 3 and ab.dtype == torch.bfloat16
+assert ab.self_attn.qkv is blk.self_attn.qkv and ab.cross_attn.o is blk.cross_attn.o and ab.ffn[2] is blk.ffn[2]
+assert ab.modulation is blk.modulation and ab.norm3 is blk.norm3
+assert sorted(blk.state_dict()) == keys and not any(p is None for p in blk.parameters())
+assert WanAttentionBlock.forward.__name__ == "fused_wan_forward"
+# blocks that do not qualify keep their own forward: plain Linears, or another attention backend
+assert "separate Linears" in adopt.why_not_adoptable(build(Linear, KsanaAttentionBackend.SAGE_ATTN))
+assert "Sage" in adopt.why_not_adoptable(build(linear.b200_fp8_ops(), KsanaAttentionBackend.TORCH_SDPA))
+plain = build(Linear, KsanaAttentionBackend.TORCH_SDPA)
+from ksana.operations.attention.backends.sdpa import SDPAImpl
+SDPAImpl.supports = staticmethod(lambda **_: True)
+from ksana.models.wan.wan_model import rope_params
+freqs = torch.cat([rope_params(1024, 44), rope_params(1024, 42), rope_params(1024, 42)], dim=1)
+for p_ in plain.parameters():
+    torch.nn.init.normal_(p_, std=0.02)
+x = torch.randn(1, 24, 256).to(torch.bfloat16); e = torch.randn(1, 1, 6, 256).to(torch.bfloat16); c = torch.randn(1, 8, 256).to(torch.bfloat16)
+with torch.no_grad():
+    y = plain(x, e, seq_lens=torch.tensor([24]), grid_sizes=torch.tensor([[2, 3, 4]]), freqs=freqs, context=c, context_lens=None,
+              step_iter=0, latent_shape=[1, 16, 2, 6, 8])
+install.uninstall()
+assert WanAttentionBlock.forward.__name__ == "forward"
+with torch.no_grad():
+    y2 = plain(x, e, seq_lens=torch.tensor([24]), grid_sizes=torch.tensor([[2, 3, 4]]), freqs=freqs, context=c, context_lens=None,
+               step_iter=0, latent_shape=[1, 16, 2, 6, 8])
+assert torch.equal(y, y2)  # the patched forward handed the non-qualifying block to the original one
+print("adopt ok")
+"""
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "adopt ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
