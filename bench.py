@@ -273,6 +273,32 @@ def exchange_check(world, rank, dev):
             "after_1_block": {"cos": -float(t[0].item()), "max_abs_rel": float(t[1].item())},
             "cos": -float(t[2].item()), "max_abs_rel": float(t[3].item())}
 
+def cpu_reference_sample(tokens, reps):
+    """Times the CPU restatement of the reference path (emulated FP8 Linear + SDPA) on one Wan-14B-shaped block
+    over `tokens` tokens; returns (TFLOP/s, seconds per block, description)."""
+    from oracle import dit_ops as D
+    cfg = W14
+    torch.set_num_threads(os.cpu_count() or 1)
+    grid = (1, 16, tokens // 16)
+    p = D.make_wan_block_params(cfg["dim"], cfg["ffn"], cfg["heads"], seed=0)
+    x = D.make_activations(tokens, cfg["dim"], seed=0)[None]
+    g = torch.Generator().manual_seed(0)
+    e = (torch.randn(1, 1, 6, cfg["dim"], generator=g) * 0.1).to(torch.bfloat16)
+    ctx = torch.randn(1, cfg["text_len"], cfg["dim"], generator=g).to(torch.bfloat16)
+    one = dict(cfg, layers=1)
+    fl = step_flops(one, tokens)
+    ts = []
+    with torch.no_grad():
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            D.wan_block_forward(p, x, e, ctx, grid, linear="fp8", attn="sdpa")
+            ts.append(time.perf_counter() - t0)
+    t = statistics.median(ts)
+    desc = (f"one Wan2.2-14B-shaped block (dim {cfg['dim']}, ffn {cfg['ffn']}, {cfg['heads']} heads) on {tokens} tokens + "
+            f"{cfg['text_len']} text tokens, torch CPU, emulated per-token/per-channel FP8 Linear + SDPA, median of {reps}")
+    return fl / t / 1e12, t, desc
+
+
 def cpu_config1_block():
     """The benchmark's CPU-runnable configuration timed whole: one Wan2.1-1.3B-shaped block (dim 1536, 12 heads, FFN 8960,
     1560 tokens, 512 text tokens) through the CPU restatement of the reference path, all host cores."""
