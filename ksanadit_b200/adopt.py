@@ -1,7 +1,8 @@
 """Runs KsanaDiT's own block modules through the fused B200 kernel sequence, on the modules' own parameters.
 
 ``install(fused_blocks=True)`` replaces ``WanAttentionBlock.forward`` (ksana/models/wan/wan_model.py:325-393) by
-``fused_wan_forward`` below.  A block built through the B200 operator registry (FP8 Linears of this package, fused
+``fused_wan_forward`` below, and ``QwenImageTransformerBlock.forward`` (ksana/models/qwen/transformer.py:196-241) by
+``fused_qwen_forward`` in the same way.  A block built through the B200 operator registry (FP8 Linears of this package, fused
 QKV projection, a Sage attention backend, 128-wide heads, RMSNorm on q / k) is *adopted*: a ``B200WanBlock`` is
 created around the block's existing sub-modules -- ``self_attn.qkv / o / norm_q / norm_k``, ``cross_attn.q / k / v / o /
 norm_q / norm_k``, ``norm3``, ``ffn[0]``, ``ffn[2]``, ``modulation`` are the same objects, nothing is copied and the
@@ -19,6 +20,7 @@ import torch
 from . import attention
 from .config import backend_value
 from .linear import B200Fp8Linear
+from .qwen_block import B200QwenBlock
 from .wan_block import HEAD, B200WanBlock
 
 _ADOPTED = "_ksana_b200_adopted"
@@ -122,3 +124,78 @@ def make_fused_wan_forward(original_forward):
 
     fused_wan_forward.__wrapped__ = original_forward
     return fused_wan_forward
+
+
+# ----------------------------------------------------------------------------- Qwen-Image dual-stream block
+
+_QWEN_NORMS = ("norm_q", "norm_k", "norm_added_q", "norm_added_k")
+
+
+class AdoptedQwenBlock(B200QwenBlock):
+    """A ``B200QwenBlock`` whose sub-modules are those of an existing QwenImageTransformerBlock module."""
+
+    def __init__(self, block):
+        torch.nn.Module.__init__(self)
+        self.zero_cond_t = bool(getattr(block, "zero_cond_t", False))
+        self.dim, self.num_heads = block.dim, block.num_attention_heads
+        self.eps = float(getattr(block.img_norm1, "eps", 1e-6))
+        self.img_mod, self.txt_mod, self.attn = block.img_mod, block.txt_mod, block.attn
+        self.img_mlp, self.txt_mlp = block.img_mlp, block.txt_mlp
+        self.dtype = block.img_mod[1].compute_dtype
+        self.ffn_dim = block.img_mlp.net[0].proj.out_features
+        self._mod_fused = None
+        self._norm_cache = {}
+
+    def _norm_weight(self, name):
+        # the reference keeps these weights in the run dtype; the kernel takes fp32 (one converted copy per weight version)
+        w = getattr(self.attn, name).weight
+        hit = self._norm_cache.get(name)
+        if hit is None or hit[0] != (w.data_ptr(), w._version):
+            hit = ((w.data_ptr(), w._version), w.detach().float().contiguous())
+            self._norm_cache[name] = hit
+        return hit[1]
+
+
+def why_not_adoptable_qwen(block) -> str | None:
+    a = getattr(block, "attn", None)
+    if a is None or not hasattr(block, "img_mod") or not hasattr(block, "txt_mlp"):
+        return "not a Qwen-Image transformer block"
+    if not hasattr(a, "to_qkv") or not hasattr(a, "add_qkv_proj"):
+        return "q / k / v are separate Linears (build the model with the B200 fusion switch installed)"
+    linears = [block.img_mod[1], block.txt_mod[1], a.to_qkv, a.add_qkv_proj, a.to_out[0], a.to_add_out,
+               block.img_mlp.net[0].proj, block.img_mlp.net[2], block.txt_mlp.net[0].proj, block.txt_mlp.net[2]]
+    if not all(isinstance(m, B200Fp8Linear) for m in linears):
+        return "a Linear of the block is not the B200 FP8 Linear"
+    if block.attention_head_dim != HEAD or block.dim != block.num_attention_heads * HEAD:
+        return f"head size {block.attention_head_dim} (only {HEAD})"
+    for n in _QWEN_NORMS:
+        w = getattr(getattr(a, n), "weight", None)
+        if w is None or w.numel() != HEAD:
+            return "q / k RMSNorm without a per-head weight"
+    cfg = getattr(getattr(a, "attention", None), "attention_config", None)
+    if cfg is None or backend_value(cfg.backend) != "sage_attention":
+        return "the block's attention backend is not the Sage backend"
+    return None
+
+
+def adopt_qwen(block):
+    cached = block.__dict__.get(_ADOPTED)
+    if cached is None:
+        cached = (AdoptedQwenBlock(block),) if why_not_adoptable_qwen(block) is None else (None,)
+        block.__dict__[_ADOPTED] = cached
+    return cached[0]
+
+
+def make_fused_qwen_forward(original_forward):
+    def fused_qwen_forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, modulate_index=None):
+        ab = adopt_qwen(self)
+        takes = (ab is not None and hidden_states.is_cuda and hidden_states.dtype == ab.dtype and hidden_states.shape[0] == 1
+                 and image_rotary_emb is not None and not torch.is_grad_enabled()
+                 and (modulate_index is not None) == ab.zero_cond_t)
+        if not takes:
+            return original_forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=image_rotary_emb,
+                                    modulate_index=modulate_index)
+        return ab(hidden_states, encoder_hidden_states, temb, image_rotary_emb=image_rotary_emb, modulate_index=modulate_index)
+
+    fused_qwen_forward.__wrapped__ = original_forward
+    return fused_qwen_forward

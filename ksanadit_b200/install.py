@@ -11,7 +11,8 @@ Hooks (all are module-level names KsanaDiT looks up at call time):
 * QKV fusion switch: ``should_use_qkv_fusion`` is looked up as a global of
   ksana/operations/fuse_qkv/fuse_qkv.py at :209 -> replaced; ``remap_qkv_weights`` gains scale handling;
 * collectives: ``all_to_all`` as imported by the model modules (wan_model.py:13, qwen/attention.py:27-28);
-* with ``fused_blocks=True`` also ``WanAttentionBlock.forward`` (wan_model.py:325-393): blocks built from the
+* with ``fused_blocks=True`` also ``WanAttentionBlock.forward`` (wan_model.py:325-393) and
+  ``QwenImageTransformerBlock.forward`` (qwen/transformer.py:196-241): blocks built from the
   operators above run as the fused kernel sequence on their own parameters (``adopt.py``), so the adaLN / RMSNorm /
   RoPE / GELU / gated-residual passes between the operator calls are fused too; other blocks keep their forward.
 
@@ -84,6 +85,14 @@ def install(patch_collectives: bool = True, fused_blocks: bool = False) -> None:
         original = wm.WanAttentionBlock.forward
         _saved["wan_forward"] = (wm.WanAttentionBlock, original)
         wm.WanAttentionBlock.forward = adopt.make_fused_wan_forward(original)
+        try:
+            qt = _ksana("ksana.models.qwen.transformer")
+        except RuntimeError:
+            qt = None
+        if qt is not None:
+            q_original = qt.QwenImageTransformerBlock.forward
+            _saved["qwen_forward"] = (qt.QwenImageTransformerBlock, q_original)
+            qt.QwenImageTransformerBlock.forward = adopt.make_fused_qwen_forward(q_original)
 
 
 def uninstall() -> None:
@@ -98,7 +107,8 @@ def uninstall() -> None:
     fq.should_use_qkv_fusion, fq.remap_qkv_weights = a, b
     for m, fn in _saved.get("a2a", []):
         m.all_to_all = fn
-    if "wan_forward" in _saved:
-        cls, fn = _saved["wan_forward"]
-        cls.forward = fn
+    for key in ("wan_forward", "qwen_forward"):
+        if key in _saved:
+            cls, fn = _saved[key]
+            cls.forward = fn
     _saved.clear()

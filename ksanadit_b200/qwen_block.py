@@ -108,6 +108,27 @@ class B200QwenBlock(torch.nn.Module):
         return self
 
     # ------------------------------------------------------------------ forward
+    def _norm_weight(self, name):
+        """fp32 [128] weight of one of the four per-head RMSNorms."""
+        return getattr(self.attn, name).weight
+
+    _rotary_tables = None  # (key, image table, text table) built from a caller's rotary embeddings
+
+    def _tables_from_rotary(self, image_rotary_emb):
+        """Rotation tables from the reference's own ``image_rotary_emb = (vid_freqs, txt_freqs)`` (complex [L, 64], one row
+        per token: QwenEmbedRope.forward, qwen/attention.py:113-142): row t of a table is token t's (cos, sin) pairs, read
+        with one position for all axes."""
+        vf, tf = image_rotary_emb
+        key = (vf.data_ptr(), tf.data_ptr(), tuple(vf.shape), tuple(tf.shape))
+        if self._rotary_tables is None or self._rotary_tables[0] != key:
+            tabs = []
+            for f in (vf, tf):
+                if not f.is_complex() or f.shape[-1] != HEAD // 2:
+                    raise _lib.KsanaB200Error("image_rotary_emb must hold complex [L, 64] tensors")
+                tabs.append(torch.view_as_real(f.reshape(-1, HEAD // 2)).to(torch.float32).contiguous())
+            self._rotary_tables = (key, tabs[0], tabs[1])
+        return (self._rotary_tables[1], 0, 0), (self._rotary_tables[2], 0, 0)
+
     def _modulation(self, st):
         """img_mod and txt_mod (transformer.py:204-211) as ONE GEMM: both are Linears of the same one-row input, and at
         one row a GEMM only streams its weight, so two launches cost twice the fixed part.  The two weights are
@@ -148,8 +169,8 @@ class B200QwenBlock(torch.nn.Module):
         its index names (the kernels take one modulation row per token), the text stream uses row 0."""
         if hidden_states.shape[0] != 1:
             raise _lib.KsanaB200Error("batch 1 only")
-        if img_grid is None:
-            raise ValueError("img_grid=(F, H, W) is required")
+        if img_grid is None and image_rotary_emb is None:
+            raise ValueError("img_grid=(F, H, W) or image_rotary_emb is required")
         img, txt = hidden_states[0], encoder_hidden_states[0]
         Li, C = img.shape  # local image rows
         Lt = txt.shape[0]
@@ -158,7 +179,14 @@ class B200QwenBlock(torch.nn.Module):
         if H % P != 0:
             raise _lib.KsanaB200Error(f"{H} heads cannot be split over {P} ranks")
         Hl = H // P
-        img_tab, txt_tab = ops.qwen_rope_tables(img_grid, Lt, device=img.device)
+        if img_grid is not None:
+            img_tab, txt_tab = ops.qwen_rope_tables(img_grid, Lt, device=img.device)
+            img_rope = (img_grid, False)
+        else:  # per-token rows taken from the caller's embeddings: one running position, rank r starts at its first row
+            img_tab, txt_tab = self._tables_from_rotary(image_rotary_emb)
+            if img_tab[0].shape[0] < P * Li or txt_tab[0].shape[0] < Lt:
+                raise _lib.KsanaB200Error("image_rotary_emb is shorter than the token sequences")
+            img_rope = ((img_tab[0].shape[0], 1, 1), True)
         st = torch.nn.functional.silu(temb)
         if st.shape[0] != (2 if self.zero_cond_t else 1) or (modulate_index is not None) != self.zero_cond_t:
             raise _lib.KsanaB200Error("a zero_cond_t block takes temb [2, C] and a modulate_index; any other block temb [1, C] and none")
@@ -176,13 +204,13 @@ class B200QwenBlock(torch.nn.Module):
         qkv = torch.empty(Lt + Li, 3 * C, dtype=self.dtype, device=img.device)
         a = self.attn
         for x, mod, lin, nq, nk, rows, tab, grid, diag, pos0 in (
-            (txt, tmod, a.add_qkv_proj, a.norm_added_q, a.norm_added_k, slice(0, Lt), txt_tab, (Lt, 1, 1), True, 0),
-            (img, imod, a.to_qkv, a.norm_q, a.norm_k, slice(Lt, Lt + Li), img_tab, img_grid, False, rank * Li),
+            (txt, tmod, a.add_qkv_proj, "norm_added_q", "norm_added_k", slice(0, Lt), txt_tab, (txt_tab[0].shape[0] if img_grid is None else Lt, 1, 1), True, 0),
+            (img, imod, a.to_qkv, "norm_q", "norm_k", slice(Lt, Lt + Li), img_tab, img_rope[0], img_rope[1], rank * Li),
         ):
             xq, sx = ops.adaln_quant_fp8(x, mod[0, 0], mod[0, 1], self.eps, round_product=True)
             lin.forward_quantized(xq, sx, self.dtype, out=qkv[rows])
-            ops.rmsnorm_rope_inplace(qkv[rows, :C], nq.weight, self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
-            ops.rmsnorm_rope_inplace(qkv[rows, C:2 * C], nk.weight, self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
+            ops.rmsnorm_rope_inplace(qkv[rows, :C], self._norm_weight(nq), self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
+            ops.rmsnorm_rope_inplace(qkv[rows, C:2 * C], self._norm_weight(nk), self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
         if P == 1:
             t = qkv.view(Lt + Li, 3, H, HEAD)
             o = ops.sage_attention(t[:, 0], t[:, 1], t[:, 2]).view(Lt + Li, C)

@@ -367,3 +367,68 @@ def test_fused_forward_on_an_adopted_reference_shaped_block(radial):
     # a call the fused path does not take goes to the original forward
     with pytest.raises(AssertionError, match="original forward"):
         fused(ref_like, x, e, step_iter=0, feta_enabled=True, **kw)
+
+
+class _RefShapedQwenBlock(torch.nn.Module):
+    """Attribute layout of KsanaDiT's QwenImageTransformerBlock built from the B200 operators (qwen/transformer.py:122-169,
+    qwen/attention.py:221-281): per-head RMSNorm weights in the run dtype, `attention.attention_config`, LayerNorms."""
+
+    def __init__(self, dim, heads, ffn, attention_config, zero_cond_t=False):
+        super().__init__()
+        from ksanadit_b200.linear import B200Fp8Linear
+        self.dim, self.num_attention_heads, self.attention_head_dim, self.zero_cond_t = dim, heads, dim // heads, zero_cond_t
+        self.img_mod = torch.nn.Sequential(torch.nn.SiLU(), B200Fp8Linear(dim, 6 * dim))
+        self.txt_mod = torch.nn.Sequential(torch.nn.SiLU(), B200Fp8Linear(dim, 6 * dim))
+        self.img_norm1 = torch.nn.LayerNorm(dim, 1e-6, elementwise_affine=False)
+        a = torch.nn.Module()
+        a.to_qkv, a.add_qkv_proj = B200Fp8Linear(dim, 3 * dim), B200Fp8Linear(dim, 3 * dim)
+        a.to_out = torch.nn.ModuleList([B200Fp8Linear(dim, dim), torch.nn.Dropout(0.0)])
+        a.to_add_out = B200Fp8Linear(dim, dim)
+        for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+            m = torch.nn.Module()
+            m.weight = torch.nn.Parameter(torch.ones(128, dtype=torch.bfloat16), requires_grad=False)
+            setattr(a, n, m)
+        a.attention = torch.nn.Module()
+        a.attention.attention_config = attention_config
+        self.attn = a
+        for s in ("img_mlp", "txt_mlp"):
+            mlp, act = torch.nn.Module(), torch.nn.Module()
+            act.proj = B200Fp8Linear(dim, ffn)
+            mlp.net = torch.nn.ModuleList([act, torch.nn.Identity(), B200Fp8Linear(ffn, dim)])
+            setattr(self, s, mlp)
+
+
+def test_fused_forward_on_an_adopted_reference_shaped_qwen_block():
+    """The adopted block takes its rotation tables from the caller's `image_rotary_emb` (complex, one row per token) and
+    gives what B200QwenBlock gives from the grid with the same weights; both match the oracle."""
+    from ksanadit_b200 import _lib, adopt
+    from ksanadit_b200.config import KsanaAttentionBackend, KsanaAttentionConfig
+    from ksanadit_b200.qwen_block import B200QwenBlock
+    dim, ffn, heads, grid, Lt = 256, 1024, 2, (1, 6, 8), 10
+    Li = grid[1] * grid[2]
+    p = D.make_qwen_block_params(dim, ffn, heads, seed=5)
+    for nm in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
+        p[nm] = p[nm].to(torch.bfloat16)
+    ours = B200QwenBlock(dim, heads, ffn, device="cuda").load_block_state_dict(_qwen_state_dict(p))
+    ref_like = _RefShapedQwenBlock(dim, heads, ffn, KsanaAttentionConfig(backend=KsanaAttentionBackend.SAGE_ATTN)).cuda()
+    missing, unexpected = ref_like.load_state_dict(ours.state_dict(), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    assert adopt.why_not_adoptable_qwen(ref_like) is None
+    fused = adopt.make_fused_qwen_forward(lambda *a, **k: (_ for _ in ()).throw(AssertionError("the original forward must not run")))
+    g = torch.Generator().manual_seed(9)
+    img = D.make_activations(Li, dim, seed=6)
+    txt = torch.randn(Lt, dim, generator=g).to(torch.bfloat16)
+    temb = torch.randn(dim, generator=g).to(torch.bfloat16)
+    ia, ta = D.qwen_rope_angles(grid, Lt)  # [L, 64] angles -> the complex per-token rows the reference's rope module returns
+    rotary = tuple(torch.polar(torch.ones_like(a_.float()), a_.float()).cuda() for a_ in (ia, ta))
+    with torch.no_grad():
+        t_grid, i_grid = ours(img[None].cuda(), txt[None].cuda(), temb[None].cuda(), img_grid=grid)
+        t_rot, i_rot = fused(ref_like, img[None].cuda(), txt[None].cuda(), temb[None].cuda(), image_rotary_emb=rotary)
+    _lib.assert_device_ok()
+    i_ref, t_ref = D.qwen_block_forward(p, img, txt, temb, ia, ta, linear="fp8", attn="sage")
+    for out, ref in ((i_rot[0].cpu().float(), i_ref.float()), (t_rot[0].cpu().float(), t_ref.float())):
+        assert cosine(out, ref) >= BLOCK_COS and max_abs_rel(out, ref) <= BLOCK_MAR
+    # same kernels, tables built two ways (fp64 formula vs the caller's fp32 cos / sin): equal up to the table's last bit
+    assert cosine(i_rot.cpu().float(), i_grid.cpu().float()) > 0.99999 and cosine(t_rot.cpu().float(), t_grid.cpu().float()) > 0.99999
+    with pytest.raises(AssertionError, match="original forward"):  # no rotary embeddings: not a call the fused path takes
+        fused(ref_like, img[None].cuda(), txt[None].cuda(), temb[None].cuda())

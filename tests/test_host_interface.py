@@ -285,6 +285,22 @@ with torch.no_grad():
     y2 = plain(x, e, seq_lens=torch.tensor([24]), grid_sizes=torch.tensor([[2, 3, 4]]), freqs=freqs, context=c, context_lens=None,
                step_iter=0, latent_shape=[1, 16, 2, 6, 8])
 assert torch.equal(y, y2)  # the patched forward handed the non-qualifying block to the original one
+# the Qwen-Image dual-stream block is adopted the same way
+install.install(fused_blocks=True)
+from ksana.models.qwen.transformer import QwenImageTransformerBlock
+ops = Ops()
+for n, c in (("Linear", linear.b200_fp8_ops()), ("LayerNorm", LayerNorm), ("RMSNorm", RMSNorm)):
+    ops.register(n, c)
+ops.register("Attn", pick_attn_op(KsanaAttentionConfig(backend=KsanaAttentionBackend.SAGE_ATTN)))
+qb = QwenImageTransformerBlock(256, 2, 128, operation_settings={{"operations": ops, "device": "cpu", "dtype": torch.bfloat16, "rms_dtype": None}})
+qkeys = sorted(qb.state_dict())
+assert adopt.why_not_adoptable_qwen(qb) is None
+qa = adopt.adopt_qwen(qb)
+assert qa.attn.to_qkv is qb.attn.to_qkv and qa.txt_mlp.net[2] is qb.txt_mlp.net[2] and qa.img_mod[1] is qb.img_mod[1]
+assert qa._norm_weight("norm_added_k").dtype == torch.float32 and sorted(qb.state_dict()) == qkeys
+assert QwenImageTransformerBlock.forward.__name__ == "fused_qwen_forward"
+install.uninstall()
+assert QwenImageTransformerBlock.forward.__name__ == "forward"
 print("adopt ok")
 """
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
