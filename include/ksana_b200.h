@@ -187,6 +187,35 @@ int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t 
                         int64_t head_stride, int block, float premul, const float* mean, void* out,
                         float* scale, ksb_stream_t stream);
 
+/* The QKV projection with row statistics: ksb_fp8_gemm with KSB_EPI_NONE that also writes, for every 256-column
+ * tile that starts below column sumsq_cols (a multiple of 256) and every row m, the sum of squares of the rounded
+ * outputs of that tile to tile_sumsq[tile_n][m] (fp32 [sumsq_cols / 256, M]).  RMSNorm over the C leading channels
+ * of a row (ksana/models/wan/wan_model.py:163-165, norm_q / norm_k on the projection output) then needs no pass
+ * over the output. */
+int ksb_fp8_gemm_rowstats(const void* a, const float* a_scale, const void* w, const float* w_scale, const void* bias,
+                          int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo, float* tile_sumsq,
+                          int64_t sumsq_cols, ksb_stream_t stream);
+/* rstd[g][m] = rsqrt(sum of the C / 256 tiles of column group g / C + eps), g < groups: fp32 [groups, M]. */
+int ksb_rowsumsq_to_rstd(const float* tile_sumsq, int64_t M, int64_t C, int groups, float eps, float* rstd,
+                         ksb_stream_t stream);
+
+/* RMSNorm (+ rotary embedding) folded into the K mean and the INT8 quantisers: what ksb_rmsnorm_rope_inplace followed
+ * by ksb_sage_kmean / ksb_sage_quant_int8 compute, byte for byte, without writing the normalised tensor (Q is read
+ * once, K twice).  norm_w: fp32 [H * 128], with row_rstd fp32 [L] = 1 / rms of each token over all heads (from
+ * ksb_rowsumsq_to_rstd, or any table); or per_head = 1: norm_w fp32 [128], 1 / rms over each head's own channels
+ * (row_rstd ignored).  The rope arguments are those of ksb_rmsnorm_rope_inplace (rope_table NULL: no rotation).
+ * Replaces norm_q / norm_k, apply_default_rope (ksana/models/wan/wan_model.py:163-174) and the quantisers inside
+ * sageattn. */
+int ksb_sage_kmean_normed(const void* k, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                          int64_t head_stride, const float* norm_w, int per_head, const float* row_rstd, float eps,
+                          const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
+                          int diag, float* partial, float* km, ksb_stream_t stream);
+int ksb_sage_quant_int8_normed(const void* x, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
+                               int64_t head_stride, int block, float premul, const float* mean, const float* norm_w,
+                               int per_head, const float* row_rstd, float eps, const float* rope_table, int table_len,
+                               int nf, int nh, int F, int Hh, int Ww, int64_t pos0, int diag, void* out, float* scale,
+                               ksb_stream_t stream);
+
 /* V quantiser: vs[h,d] = absmax over tokens / 448 (1 if zero); vt[h,d,l] = e4m3(float(v) * (448/absmax)), token
  * axis contiguous and zero-padded to Lpad.  amax: fp32 scratch [H*D] (overwritten). */
 int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride,
@@ -213,6 +242,7 @@ int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H,
  * Replaces `sageattn(q, k, v, tensor_layout="NHD")` (sage_attn.py:75-81) and
  * `block_sparse_sage2_attn_cuda(q, k, v, mask_id=...)` (radial_sage_attn/radial_sage_attn.py:170-176).
  *   q8 [H,Lq_pad,128], qs [H,Lq_pad/128], k8 [H,Lk_pad,128], ks [H,Lk_pad/64], vt [H,128,Lk_pad], vs [H,128]
+ *   (ks 8-byte aligned: the two 64-key scales of a 128-key tile are read as one pair)
  *   out[l,h,:] (half, element strides out_token_stride / out_head_stride) for l < Lq.
  * Block-sparse: tile_offsets int32 [Lq_pad/128 + 1] and tile_entries int32 [nnz] (shared by all heads);
  * entry = kv_tile*4 + keep bits (bit0: tokens 0-63 of the 128-token tile, bit1: tokens 64-127), ascending

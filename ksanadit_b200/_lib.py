@@ -48,6 +48,14 @@ SIGNATURES = {
     "ksb_fp8_gemm_qkv_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                          c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p]),
     "ksb_rowsumsq_to_rstd_scatter": (c_int, [c_void_p, c_int64, c_int64, c_float, c_void_p, c_int, c_int, c_void_p]),
+    "ksb_fp8_gemm_rowstats": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int,
+                                      c_int64, c_void_p, c_int64, c_void_p]),
+    "ksb_rowsumsq_to_rstd": (c_int, [c_void_p, c_int64, c_int64, c_int, c_float, c_void_p, c_void_p]),
+    "ksb_sage_kmean_normed": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_float,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "ksb_sage_quant_int8_normed": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_void_p,
+                                           c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64,
+                                           c_int, c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -204,6 +204,35 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 64 consecutive 32-bit columns in one instruction, into chunks HALF*2 and HALF*2+1 of r
+// (r[c][i] = column 32 c + i of the 128-column block that starts 64 * HALF columns before taddr).
+template <int HALF>
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[4][32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      " %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      " %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[2 * HALF + 0][0]), "=r"(r[2 * HALF + 0][1]), "=r"(r[2 * HALF + 0][2]), "=r"(r[2 * HALF + 0][3]),
+        "=r"(r[2 * HALF + 0][4]), "=r"(r[2 * HALF + 0][5]), "=r"(r[2 * HALF + 0][6]), "=r"(r[2 * HALF + 0][7]),
+        "=r"(r[2 * HALF + 0][8]), "=r"(r[2 * HALF + 0][9]), "=r"(r[2 * HALF + 0][10]), "=r"(r[2 * HALF + 0][11]),
+        "=r"(r[2 * HALF + 0][12]), "=r"(r[2 * HALF + 0][13]), "=r"(r[2 * HALF + 0][14]), "=r"(r[2 * HALF + 0][15]),
+        "=r"(r[2 * HALF + 0][16]), "=r"(r[2 * HALF + 0][17]), "=r"(r[2 * HALF + 0][18]), "=r"(r[2 * HALF + 0][19]),
+        "=r"(r[2 * HALF + 0][20]), "=r"(r[2 * HALF + 0][21]), "=r"(r[2 * HALF + 0][22]), "=r"(r[2 * HALF + 0][23]),
+        "=r"(r[2 * HALF + 0][24]), "=r"(r[2 * HALF + 0][25]), "=r"(r[2 * HALF + 0][26]), "=r"(r[2 * HALF + 0][27]),
+        "=r"(r[2 * HALF + 0][28]), "=r"(r[2 * HALF + 0][29]), "=r"(r[2 * HALF + 0][30]), "=r"(r[2 * HALF + 0][31]),
+        "=r"(r[2 * HALF + 1][0]), "=r"(r[2 * HALF + 1][1]), "=r"(r[2 * HALF + 1][2]), "=r"(r[2 * HALF + 1][3]),
+        "=r"(r[2 * HALF + 1][4]), "=r"(r[2 * HALF + 1][5]), "=r"(r[2 * HALF + 1][6]), "=r"(r[2 * HALF + 1][7]),
+        "=r"(r[2 * HALF + 1][8]), "=r"(r[2 * HALF + 1][9]), "=r"(r[2 * HALF + 1][10]), "=r"(r[2 * HALF + 1][11]),
+        "=r"(r[2 * HALF + 1][12]), "=r"(r[2 * HALF + 1][13]), "=r"(r[2 * HALF + 1][14]), "=r"(r[2 * HALF + 1][15]),
+        "=r"(r[2 * HALF + 1][16]), "=r"(r[2 * HALF + 1][17]), "=r"(r[2 * HALF + 1][18]), "=r"(r[2 * HALF + 1][19]),
+        "=r"(r[2 * HALF + 1][20]), "=r"(r[2 * HALF + 1][21]), "=r"(r[2 * HALF + 1][22]), "=r"(r[2 * HALF + 1][23]),
+        "=r"(r[2 * HALF + 1][24]), "=r"(r[2 * HALF + 1][25]), "=r"(r[2 * HALF + 1][26]), "=r"(r[2 * HALF + 1][27]),
+        "=r"(r[2 * HALF + 1][28]), "=r"(r[2 * HALF + 1][29]), "=r"(r[2 * HALF + 1][30]), "=r"(r[2 * HALF + 1][31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -287,10 +316,21 @@ template <typename T> struct HalfOps;
 template <> struct HalfOps<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+  // two values packed in a 32-bit word (low half first), same rounding as from_f
+  static __device__ __forceinline__ float2 unpack2(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
+  static __device__ __forceinline__ uint32_t pack2(float2 v) {
+    const __nv_bfloat162 h = __float22bfloat162_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
 };
 template <> struct HalfOps<__half> {
   static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float2 unpack2(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
+  static __device__ __forceinline__ uint32_t pack2(float2 v) {
+    const __half2 h = __float22half2_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
 };
 
 __device__ __forceinline__ float warp_max(float v) {

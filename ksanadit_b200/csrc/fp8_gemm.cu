@@ -60,6 +60,7 @@ struct Params {
   void* peers[KSB_MAX_PEERS];
   int n_peers, rank, heads_per_peer, C;
   float* tile_sumsq;
+  int sumsq_cols;   // tiles that start below this column write their row sums of squares (any epilogue that stores rows)
   int fetch_ahead;  // gated-residual epilogue: fetch residual / gate one chunk ahead (short main loops)
 };
 
@@ -205,6 +206,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const T* rrow = p.resid ? static_cast<const T*>(p.resid) + static_cast<int64_t>(row) * p.ldr + tn * BN : nullptr;
       const T* grow = (p.gate && p.gate_rows != 1) ? static_cast<const T*>(p.gate) + static_cast<int64_t>(row / p.rows_per_gate) * p.N + tn * BN : nullptr;
       const bool scatter = p.epilogue == KSB_EPI_SCATTER_HEADS;
+      const bool want_ssq = p.tile_sumsq != nullptr && tn * BN < p.sumsq_cols;
       float ssq = 0.f;
       // The residual (and a per-row gate) are fetched one 32-column chunk ahead when the main loop is short
       // (K <= 8192): a thread reads its own row, so these are latency-bound scattered loads, and with 40 k-steps
@@ -281,6 +283,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 }
               } else {
                 *reinterpret_cast<uint4*>(orow + cb) = o;
+                if (want_ssq) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float v = HalfOps<T>::to_f(ot[i]);
+                    ssq = fmaf(v, v, ssq);
+                  }
+                }
               }
             }
           }
@@ -296,7 +305,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         }
       }
-      if (scatter && row_ok && p.tile_sumsq && tn * BN < 2 * p.C) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
+      if (want_ssq && row_ok) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
@@ -337,7 +346,7 @@ extern "C" int ksb_fp8_gemm_qkv_scatter(const void* a, const float* a_scale, con
     if (!peer_out[i] || !aligned16(peer_out[i])) return fail(KSB_ERR_INVALID, "peer buffer %d null or unaligned", i);
     p.peers[i] = peer_out[i];
   }
-  p.n_peers = n_peers; p.rank = rank; p.heads_per_peer = (int)(heads / n_peers); p.C = (int)C; p.tile_sumsq = tile_sumsq;
+  p.n_peers = n_peers; p.rank = rank; p.heads_per_peer = (int)(heads / n_peers); p.C = (int)C; p.tile_sumsq = tile_sumsq; p.sumsq_cols = (int)(2 * C);
   return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -367,6 +376,25 @@ extern "C" int ksb_fp8_gemm(const void* a, const float* a_scale, const void* w, 
   p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = out; p.ldo = ldo; p.epilogue = epilogue;
   p.resid = resid; p.ldr = ldr; p.gate = gate; p.gate_rows = gate_rows;
   p.rows_per_gate = (gate && gate_rows > 0) ? static_cast<int>(M / gate_rows) : 1;
+  return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ksb_fp8_gemm_rowstats(const void* a, const float* a_scale, const void* w, const float* w_scale,
+                                     const void* bias, int64_t M, int64_t N, int64_t K, void* out, int dtype, int64_t ldo,
+                                     float* tile_sumsq, int64_t sumsq_cols, ksb_stream_t stream) {
+  if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
+  if (M <= 0 || N <= 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return fail(KSB_ERR_INVALID, "bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (K % 16 != 0 || N % 8 != 0) return fail(KSB_ERR_INVALID, "K must be a multiple of 16 and N of 8 (K=%lld N=%lld)", (long long)K, (long long)N);
+  if (!a || !a_scale || !w || !w_scale || !out || !tile_sumsq) return fail(KSB_ERR_INVALID, "null pointer");
+  if (ldo < N || ldo % 8 != 0 || !aligned16(out)) return fail(KSB_ERR_INVALID, "out must be 16-byte aligned with ldo >= N, ldo %% 8 == 0");
+  if (sumsq_cols <= 0 || sumsq_cols > N || sumsq_cols % gemm::BN != 0)
+    return fail(KSB_ERR_INVALID, "sumsq_cols must be a positive multiple of %d and <= N", gemm::BN);
+  gemm::Params p{};
+  p.rows_per_gate = 1;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.sa = a_scale; p.sw = w_scale; p.bias = bias; p.out = out; p.ldo = ldo; p.epilogue = KSB_EPI_NONE;
+  p.tile_sumsq = tile_sumsq; p.sumsq_cols = (int)sumsq_cols;
   return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
 }
 

@@ -236,6 +236,18 @@ __global__ void rstd_scatter_kernel(const float* __restrict__ tile_sumsq, int ti
   for (int d = 0; d < n_peers; ++d) peers.p[d][which * L_all + (int64_t)rank * M + m] = r;
 }
 
+// x = q * d + r for 0 <= x < 2^24 (exact in fp32): the estimate from the reciprocal is within one of the quotient
+__device__ __forceinline__ void divmod_small(int x, int d, float inv_d, int& q, int& r) {
+  q = static_cast<int>(static_cast<float>(x) * inv_d);
+  r = x - q * d;
+  if (r < 0) { r += d; --q; } else if (r >= d) { r -= d; ++q; }
+}
+
+// (a, b) rotated by (cos, sin): the operation order both norm/RoPE kernels share, so that their results are the same bits
+__device__ __forceinline__ float2 rope_pair(float a, float b, float2 cs) {
+  return __ffma2_rn(make_float2(-b, b), make_float2(cs.y, cs.x), __fmul2_rn(make_float2(a, a), cs));
+}
+
 template <typename T, bool ROPE, bool PER_HEAD, int NV>
 __global__ void __launch_bounds__(NR_THREADS, NV <= 5 ? 6 : 4) rmsnorm_rope_kernel(T* __restrict__ x, int64_t L, int C, int64_t ld,
                                                                      const float* __restrict__ w, float eps, RopeGrid rg,
@@ -261,7 +273,7 @@ __global__ void __launch_bounds__(NR_THREADS, NV <= 5 ? 6 : 4) rmsnorm_rope_kern
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float f = HalfOps<T>::to_f(t[e]);
-          hs += f * f;
+          hs = __fmaf_rn(f, f, hs);
         }
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
@@ -340,10 +352,9 @@ __global__ void __launch_bounds__(NR_THREADS, NV <= 5 ? 6 : 4) rmsnorm_rope_kern
         if (ROPE && rotate) {
 #pragma unroll
           for (int e = 0; e < 8; e += 2) {
-            const float2 cssn = rot[e >> 1];
-            const float a = y[e], b = y[e + 1];
-            y[e] = a * cssn.x - b * cssn.y;
-            y[e + 1] = a * cssn.y + b * cssn.x;
+            const float2 yr = rope_pair(y[e], y[e + 1], rot[e >> 1]);
+            y[e] = yr.x;
+            y[e + 1] = yr.y;
           }
         }
         uint4 o;
@@ -354,6 +365,229 @@ __global__ void __launch_bounds__(NR_THREADS, NV <= 5 ? 6 : 4) rmsnorm_rope_kern
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------------- norm + RoPE inside the quantisers
+// The same RMSNorm (+ rotary embedding) as rmsnorm_rope_kernel, applied to a tile of 128 tokens x one head as it is
+// read by a quantiser, so that the normalised tensor is never written: Q is read once, K twice (its column means
+// first).  The 1 / rms of a token over all heads comes from a table (written from the producing GEMM's per-tile sums
+// of squares, or by another rank under the fused exchange); with PER_HEAD it is taken over the head's own 128
+// channels, which the 16 lanes holding a token's vectors reduce among themselves.  The rounding points are those of
+// the in-place kernel (norm output rounded to half, rotation in fp32, rounded to half), so the bytes are the same as
+// running that kernel and then the plain quantiser with the same table.
+struct NormSpec {
+  const float* w;         // norm weight: [H * 128], or [128] with per_head
+  const float* row_rstd;  // [L]; unused with per_head
+  float eps;
+  RopeGrid rg;            // rg.table == nullptr: no rotation
+  int per_frame;          // rg.Hh * rg.Ww, with the reciprocals the position decoding uses
+  float inv_per_frame, inv_w;
+};
+
+constexpr int NQ_THREADS = 512;  // 32 token lanes x 16 column groups of 8 channels; 4 vectors per thread
+
+// Loads the thread's four vectors of tile (l0, h) and replaces them by the normalised (and rotated) values.
+template <typename T, bool PER_HEAD>
+__device__ __forceinline__ void load_normed_tile(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs, int h, int64_t l0,
+                                                 const NormSpec& ns, uint4 (&raw)[4]) {
+  const int cg = threadIdx.x & 15, tl = threadIdx.x >> 4;
+  const int c = cg * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t l = l0 + tl + 32 * i;
+    raw[i] = (l < L) ? *reinterpret_cast<const uint4*>(x + l * ts + (int64_t)h * hs + c) : make_uint4(0, 0, 0, 0);
+  }
+  float rstd[4];
+  if (!PER_HEAD) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t l = l0 + tl + 32 * i;
+      rstd[i] = (l < L) ? ns.row_rstd[l] : 0.f;
+    }
+  }
+  float2 w2[4];
+  {
+    const float* wp = ns.w + (PER_HEAD ? 0 : h * D) + c;
+    const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
+    w2[0] = make_float2(w0.x, w0.y); w2[1] = make_float2(w0.z, w0.w); w2[2] = make_float2(w1.x, w1.y); w2[3] = make_float2(w1.z, w1.w);
+  }
+  const int p0 = c >> 1;  // first of the four rotation pairs of these 8 channels
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t l = l0 + tl + 32 * i;
+    const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);
+    float2 f[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) f[q] = HalfOps<T>::unpack2(wd[q]);
+    float r;
+    if (PER_HEAD) {
+      float hsum = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        hsum = __fmaf_rn(f[q].x, f[q].x, hsum);
+        hsum = __fmaf_rn(f[q].y, f[q].y, hsum);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) hsum += __shfl_xor_sync(0xffffffffu, hsum, o);  // every lane takes part, also past L
+      r = rsqrtf(hsum / (float)D + ns.eps);
+    } else {
+      r = rstd[i];
+    }
+    if (l >= L) continue;
+    const float2 r2 = make_float2(r, r);
+    uint32_t nw[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) nw[q] = HalfOps<T>::pack2(__fmul2_rn(__fmul2_rn(f[q], r2), w2[q]));  // norm output, rounded to half
+    if (ns.rg.table) {
+      const int pos = static_cast<int>(ns.rg.pos0 + l);
+      int cf, rem, ch, cw;
+      divmod_small(pos, ns.per_frame, ns.inv_per_frame, cf, rem);
+      if (cf < ns.rg.F) {
+        divmod_small(rem, ns.rg.Ww, ns.inv_w, ch, cw);
+        if (ns.rg.diag) ch = cw = cf;
+        // pairs p0 .. p0+3 as two 16-byte table reads; a pair whose axis differs from its neighbour's is fetched on its own
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int pr = p0 + 2 * hf;
+          const int c0 = pr < ns.rg.nf ? cf : (pr < ns.rg.nf + ns.rg.nh ? ch : cw);
+          const int c1 = pr + 1 < ns.rg.nf ? cf : (pr + 1 < ns.rg.nf + ns.rg.nh ? ch : cw);
+          const float4 t4 = *reinterpret_cast<const float4*>(ns.rg.table + (int64_t)c0 * 64 + pr);
+          float2 cs0 = make_float2(t4.x, t4.y), cs1 = make_float2(t4.z, t4.w);
+          if (c1 != c0) cs1 = ns.rg.table[(int64_t)c1 * 64 + pr + 1];
+          const float2 y0 = HalfOps<T>::unpack2(nw[2 * hf]), y1 = HalfOps<T>::unpack2(nw[2 * hf + 1]);
+          nw[2 * hf] = HalfOps<T>::pack2(rope_pair(y0.x, y0.y, cs0));
+          nw[2 * hf + 1] = HalfOps<T>::pack2(rope_pair(y1.x, y1.y, cs1));
+        }
+      }
+    }
+    raw[i] = make_uint4(nw[0], nw[1], nw[2], nw[3]);
+  }
+}
+
+// Column sums of the normalised K over chunks of MEAN_CHUNK tokens: grid (chunks, H), partial[chunk][h][d].
+template <typename T, bool PER_HEAD>
+__global__ void __launch_bounds__(NQ_THREADS, 2) normed_colsum_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs, NormSpec ns,
+                                                                       float* __restrict__ partial, int H) {
+  __shared__ float red[32][D + 1];
+  const int h = blockIdx.y, chunk = blockIdx.x;
+  const int cg = threadIdx.x & 15, tl = threadIdx.x >> 4;
+  float2 acc[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) acc[q] = make_float2(0.f, 0.f);
+  for (int tile = 0; tile < MEAN_CHUNK / 128; ++tile) {
+    const int64_t l0 = (int64_t)chunk * MEAN_CHUNK + tile * 128;
+    if (l0 >= L) break;
+    uint4 raw[4];
+    load_normed_tile<T, PER_HEAD>(x, L, ts, hs, h, l0, ns, raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);  // rows past L hold zeros
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[q] = __fadd2_rn(acc[q], HalfOps<T>::unpack2(wd[q]));
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    red[tl][cg * 8 + 2 * q] = acc[q].x;
+    red[tl][cg * 8 + 2 * q + 1] = acc[q].y;
+  }
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float r = red[0][threadIdx.x];
+#pragma unroll
+    for (int j = 1; j < 32; ++j) r += red[j][threadIdx.x];
+    partial[((int64_t)chunk * H + h) * D + threadIdx.x] = r;
+  }
+}
+
+// Norm (+ RoPE) + INT8 block quantiser over a tile of 128 tokens x one head: grid (Lpad / 128, H).
+// NB = 1: one 128-token block (Q: premul, no mean); NB = 2: two 64-token blocks (K: mean subtracted).
+template <typename T, int NB, bool PER_HEAD>
+__global__ void __launch_bounds__(NQ_THREADS, 2) normed_int8_quant_kernel(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs, NormSpec ns,
+                                                                           float premul, const float* __restrict__ mean,
+                                                                           int8_t* __restrict__ out, float* __restrict__ scale, int64_t Lpad) {
+  __shared__ float red[NB][NQ_THREADS / 32];
+  const int h = blockIdx.y;
+  const int64_t l0 = (int64_t)blockIdx.x * 128;
+  const int cg = threadIdx.x & 15, tl = threadIdx.x >> 4;
+  const int c = cg * 8;
+  uint4 raw[4];
+  load_normed_tile<T, PER_HEAD>(x, L, ts, hs, h, l0, ns, raw);
+  float2 nmu[4];  // minus the mean: x - mu and x + (-mu) are the same number
+#pragma unroll
+  for (int q = 0; q < 4; ++q) nmu[q] = mean ? make_float2(-mean[h * D + c + 2 * q], -mean[h * D + c + 2 * q + 1]) : make_float2(0.f, 0.f);
+  const float2 pm2 = make_float2(premul, premul);
+  auto value = [&](uint32_t wd, int q) -> float2 {
+    float2 v = HalfOps<T>::unpack2(wd);
+    if (mean) v = __fadd2_rn(v, nmu[q]);
+    if (premul != 0.f) v = __fmul2_rn(v, pm2);
+    return v;
+  };
+  float am[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) am[b] = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (l0 + tl + 32 * i < L) {
+      const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);
+      float a = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 v = value(wd[q], q);
+        a = fmax3(a, fabsf(v.x), fabsf(v.y));
+      }
+      const int b = NB == 2 ? (i >> 1) : 0;  // tokens tl + 32 i: i = 0, 1 are the first 64
+      am[b] = fmaxf(am[b], a);
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    am[b] = warp_max(am[b]);
+    if ((threadIdx.x & 31) == 0) red[b][threadIdx.x >> 5] = am[b];
+  }
+  __syncthreads();
+  float inv[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    float a = red[b][0];
+#pragma unroll
+    for (int i = 1; i < NQ_THREADS / 32; ++i) a = fmaxf(a, red[b][i]);
+    inv[b] = (a > 0.f) ? __fdiv_rn(127.f, a) : 1.f;
+    if (threadIdx.x == 0) scale[(int64_t)h * (Lpad / 128 * NB) + (int64_t)blockIdx.x * NB + b] = (a > 0.f) ? __fdiv_rn(a, 127.f) : 1.f;
+  }
+  // rounding by the magic addend: see int8_block_quant_kernel
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = tl + 32 * i;
+    const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);
+    const float iv = inv[NB == 2 ? (i >> 1) : 0];
+    uint32_t t[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float2 v = make_float2(0.f, 0.f);  // padding rows quantise to 0 whatever the mean
+      if (l0 + r < L) v = value(wd[q], q);
+      // scalar on purpose: the product must be rounded before the addition (a packed multiply followed by a packed
+      // add was observed to round like one fused operation, which breaks ties such as 63.5 the other way)
+      t[2 * q] = __float_as_uint(__fadd_rn(__fmul_rn(v.x, iv), 12582912.f));
+      t[2 * q + 1] = __float_as_uint(__fadd_rn(__fmul_rn(v.y, iv), 12582912.f));
+    }
+    uint32_t w[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+      w[g] = __byte_perm(__byte_perm(t[4 * g], t[4 * g + 1], 0x0040), __byte_perm(t[4 * g + 2], t[4 * g + 3], 0x0040), 0x5410);
+    *reinterpret_cast<uint2*>(out + ((int64_t)h * Lpad + l0 + r) * D + c) = make_uint2(w[0], w[1]);
+  }
+}
+
+// rstd[g][m] = rsqrt(sum over the tiles of column group g of tile_sumsq[tile][m] / C + eps)
+__global__ void rstd_finish_kernel(const float* __restrict__ tile_sumsq, int tiles_per_group, int groups, int M, int C, float eps,
+                                   float* __restrict__ rstd) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups * M) return;
+  const int g = i / M, m = i - g * M;
+  float s = 0.f;
+  for (int t = 0; t < tiles_per_group; ++t) s += tile_sumsq[(int64_t)(g * tiles_per_group + t) * M + m];
+  rstd[i] = rsqrtf(s / (float)C + eps);
 }
 
 // ---------------------------------------------------------------------------------- built-in scratch
@@ -389,6 +623,34 @@ int validate(const void* x, int dtype, int64_t L, int64_t H, int64_t Dh, int64_t
   if (Dh != D) return fail(KSB_ERR_UNSUPPORTED, "head size %lld is not supported (only 128)", (long long)Dh);
   if (L <= 0 || H <= 0 || H > 65535) return fail(KSB_ERR_INVALID, "bad shape L=%lld H=%lld", (long long)L, (long long)H);
   if (!x || !aligned16(x) || ts % 8 != 0 || hs % 8 != 0) return fail(KSB_ERR_INVALID, "input must be 16-byte aligned with strides multiple of 8 elements");
+  return 0;
+}
+
+// Fills a RopeGrid from the C-ABI arguments (rope_table == nullptr: no rotation).
+int make_rope_grid(RopeGrid& rg, const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0, int diag) {
+  rg = RopeGrid{};
+  if (!rope_table) return 0;
+  if (nf < 0 || nh < 0 || nf + nh > 64 || F <= 0 || Hh <= 0 || Ww <= 0) return fail(KSB_ERR_INVALID, "bad rope grid");
+  if (F > table_len || (!diag && (Hh > table_len || Ww > table_len))) return fail(KSB_ERR_INVALID, "rope table too short for the grid");
+  if (diag && (Hh != 1 || Ww != 1)) return fail(KSB_ERR_INVALID, "diag positions need a grid of (F, 1, 1)");
+  if (!aligned16(rope_table)) return fail(KSB_ERR_INVALID, "rope table must be 16-byte aligned");
+  rg.table = reinterpret_cast<const float2*>(rope_table); rg.table_len = table_len; rg.nf = nf; rg.nh = nh;
+  rg.F = F; rg.Hh = Hh; rg.Ww = Ww; rg.pos0 = pos0; rg.diag = diag ? 1 : 0;
+  return 0;
+}
+
+int make_norm_spec(NormSpec& ns, int64_t L, const float* norm_w, int per_head, const float* row_rstd, float eps, const float* rope_table,
+                   int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0, int diag) {
+  if (!norm_w || !aligned16(norm_w)) return fail(KSB_ERR_INVALID, "norm weight null or unaligned");
+  if (!per_head && !row_rstd) return fail(KSB_ERR_INVALID, "a norm over all heads needs the row_rstd table");
+  ns.w = norm_w; ns.row_rstd = per_head ? nullptr : row_rstd; ns.eps = eps;
+  if (int rc = make_rope_grid(ns.rg, rope_table, table_len, nf, nh, F, Hh, Ww, pos0, diag)) return rc;
+  if (rope_table) {
+    if (pos0 < 0 || pos0 + L > (1 << 24)) return fail(KSB_ERR_INVALID, "token positions must stay below 2^24");
+    ns.per_frame = Hh * Ww;
+    ns.inv_per_frame = 1.0f / (float)ns.per_frame;
+    ns.inv_w = 1.0f / (float)Ww;
+  }
   return 0;
 }
 
@@ -450,13 +712,7 @@ int ksb_rmsnorm_rope_inplace(void* x, int dtype, int64_t L, int64_t C, int64_t l
   if ((colsum_partial == nullptr) != (colmean == nullptr)) return fail(KSB_ERR_INVALID, "colsum_partial and colmean go together");
   if (row_rstd && per_head) return fail(KSB_ERR_INVALID, "row_rstd and per_head exclude each other");
   prep::RopeGrid rg{};
-  if (rope_table) {
-    if (nf < 0 || nh < 0 || nf + nh > 64 || F <= 0 || Hh <= 0 || Ww <= 0) return fail(KSB_ERR_INVALID, "bad rope grid");
-    if (F > table_len || (!diag && (Hh > table_len || Ww > table_len))) return fail(KSB_ERR_INVALID, "rope table too short for the grid");
-    if (diag && (Hh != 1 || Ww != 1)) return fail(KSB_ERR_INVALID, "diag positions need a grid of (F, 1, 1)");
-    rg.table = reinterpret_cast<const float2*>(rope_table); rg.table_len = table_len; rg.nf = nf; rg.nh = nh;
-    rg.F = F; rg.Hh = Hh; rg.Ww = Ww; rg.pos0 = pos0; rg.diag = diag ? 1 : 0;
-  }
+  if (int rc = prep::make_rope_grid(rg, rope_table, table_len, nf, nh, F, Hh, Ww, pos0, diag)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t cap = (int64_t)sm_count() * 16;
   const int blocks = (int)(L < cap ? L : cap);
@@ -507,6 +763,55 @@ int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t 
   }
 #undef KSB_LAUNCH_Q
   return check_launch("int8 block quantiser");
+}
+
+int ksb_rowsumsq_to_rstd(const float* tile_sumsq, int64_t M, int64_t C, int groups, float eps, float* rstd, ksb_stream_t stream) {
+  if (!tile_sumsq || !rstd || M <= 0 || C <= 0 || C % 256 != 0 || groups < 1 || groups * M > INT32_MAX) return fail(KSB_ERR_INVALID, "bad arguments");
+  const int n = (int)(groups * M);
+  prep::rstd_finish_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(tile_sumsq, (int)(C / 256), groups, (int)M, (int)C, eps, rstd);
+  return check_launch("rstd from tile sums");
+}
+
+int ksb_sage_kmean_normed(const void* k, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,
+                          const float* norm_w, int per_head, const float* row_rstd, float eps, const float* rope_table, int table_len,
+                          int nf, int nh, int F, int Hh, int Ww, int64_t pos0, int diag, float* partial, float* km, ksb_stream_t stream) {
+  if (int rc = prep::validate(k, dtype, L, H, D, token_stride, head_stride)) return rc;
+  if (!partial || !km) return fail(KSB_ERR_INVALID, "null pointer");
+  prep::NormSpec ns{};
+  if (int rc = prep::make_norm_spec(ns, L, norm_w, per_head, row_rstd, eps, rope_table, table_len, nf, nh, F, Hh, Ww, pos0, diag)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int chunks = (int)((L + prep::MEAN_CHUNK - 1) / prep::MEAN_CHUNK);
+  dim3 grid(chunks, (unsigned)H);
+#define KSB_LAUNCH_CS(T, P) prep::normed_colsum_kernel<T, P><<<grid, prep::NQ_THREADS, 0, st>>>(static_cast<const T*>(k), L, token_stride, head_stride, ns, partial, (int)H)
+  if (dtype == KSB_BF16) { if (per_head) KSB_LAUNCH_CS(__nv_bfloat16, true); else KSB_LAUNCH_CS(__nv_bfloat16, false); }
+  else { if (per_head) KSB_LAUNCH_CS(__half, true); else KSB_LAUNCH_CS(__half, false); }
+#undef KSB_LAUNCH_CS
+  if (int rc = check_launch("normed k column sums")) return rc;
+  const int HD = (int)(H * D);
+  prep::mean_finish_kernel<<<(HD + 255) / 256, 256, 0, st>>>(partial, chunks, HD, 1.0f / (float)L, km);
+  return check_launch("k mean (finish)");
+}
+
+int ksb_sage_quant_int8_normed(const void* x, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,
+                               int block, float premul, const float* mean, const float* norm_w, int per_head, const float* row_rstd,
+                               float eps, const float* rope_table, int table_len, int nf, int nh, int F, int Hh, int Ww, int64_t pos0,
+                               int diag, void* out, float* scale, ksb_stream_t stream) {
+  if (int rc = prep::validate(x, dtype, L, H, D, token_stride, head_stride)) return rc;
+  if (block != 128 && block != 64) return fail(KSB_ERR_INVALID, "block must be 128 or 64");
+  if (!out || !scale || !aligned16(out)) return fail(KSB_ERR_INVALID, "null or unaligned output");
+  prep::NormSpec ns{};
+  if (int rc = prep::make_norm_spec(ns, L, norm_w, per_head, row_rstd, eps, rope_table, table_len, nf, nh, F, Hh, Ww, pos0, diag)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t Lpad = prep::pad128(L);
+  dim3 grid((unsigned)(Lpad / 128), (unsigned)H);
+  int8_t* o = static_cast<int8_t*>(out);
+#define KSB_LAUNCH_NQ(T, NB, P) prep::normed_int8_quant_kernel<T, NB, P><<<grid, prep::NQ_THREADS, 0, st>>>(static_cast<const T*>(x), L, token_stride, head_stride, ns, premul, mean, o, scale, Lpad)
+#define KSB_LAUNCH_NQ2(T) do { if (block == 128) { if (per_head) KSB_LAUNCH_NQ(T, 1, true); else KSB_LAUNCH_NQ(T, 1, false); } \
+                               else { if (per_head) KSB_LAUNCH_NQ(T, 2, true); else KSB_LAUNCH_NQ(T, 2, false); } } while (0)
+  if (dtype == KSB_BF16) KSB_LAUNCH_NQ2(__nv_bfloat16); else KSB_LAUNCH_NQ2(__half);
+#undef KSB_LAUNCH_NQ2
+#undef KSB_LAUNCH_NQ
+  return check_launch("normed int8 block quantiser");
 }
 
 int ksb_sage_quant_v_fp8(const void* v, int dtype, int64_t L, int64_t H, int64_t D, int64_t token_stride, int64_t head_stride,

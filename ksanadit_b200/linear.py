@@ -136,6 +136,11 @@ class B200Fp8Linear(torch.nn.Linear):
         return ops.fp8_gemm(xq, sx, self.weight.data, self.weight_scale_vector(), self.bias, out_dtype=out_dtype, epilogue=epilogue,
                             resid=resid, gate=gate, out=out)
 
+    def forward_quantized_rowstats(self, xq, sx, out_dtype, sumsq_cols):
+        """forward_quantized that also returns the per-tile row sums of squares of the first ``sumsq_cols`` output
+        columns ([sumsq_cols / 256, M] fp32): the statistics of an RMSNorm that follows this projection."""
+        return ops.fp8_gemm_rowstats(xq, sx, self.weight.data, self.weight_scale_vector(), self.bias, sumsq_cols, out_dtype=out_dtype)
+
     # API kept from ScaledFp8Linear (fp8_linear.py:138-154)
     def convert_weight(self, weight, inplace=False, **kwargs):
         s = self.weight_scale_vector().to(weight.dtype)[:, None]

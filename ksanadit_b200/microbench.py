@@ -106,15 +106,40 @@ def run_prepass(a):
     grid = (21, max(1, L // 21 // 80), 80)
     t3 = qkv.view(L, 3, H, 128)
     km = torch.zeros(H, 128, device="cuda")
+    sums = qkv[:, :2 * C].float().view(L, 2 * C // 256, 256).pow(2).sum(-1).t().contiguous() if C % 256 == 0 else None
+    rstd = torch.rsqrt(qkv[:, :2 * C].float().view(L, 2, C).pow(2).mean(-1) + 1e-6).t().contiguous()
     for name, fn, by in (
         ("rmsnorm_rope_inplace(k, +mean)", lambda: ops.rmsnorm_rope_inplace(qkv[:, C:2 * C], w, 1e-6, rope, grid, want_mean=True), L * C * 4),
         ("sage_quant_int8(q)", lambda: ops.sage_quant_int8(t3[:, 0], 128, premul=0.1), L * C * 3),
         ("sage_quant_int8(k)", lambda: ops.sage_quant_int8(t3[:, 1], 64, mean=km), L * C * 3),
         ("sage_quant_v", lambda: ops.sage_quant_v(t3[:, 2]), L * C * 5),
         ("sage_kmean", lambda: ops.sage_kmean(t3[:, 1]), L * C * 2),
+        ("sage_kmean_normed(k)", lambda: ops.sage_kmean_normed(t3[:, 1], w, 1e-6, rope, grid, row_rstd=rstd[1]), L * C * 2),
+        ("sage_quant_int8_normed(q)", lambda: ops.sage_quant_int8_normed(t3[:, 0], 128, w, premul=0.1, rope=rope, grid=grid, row_rstd=rstd[0]), L * C * 3),
+        ("sage_quant_int8_normed(k)", lambda: ops.sage_quant_int8_normed(t3[:, 1], 64, w, mean=km, rope=rope, grid=grid, row_rstd=rstd[1]), L * C * 3),
     ):
         t = timeit(fn, a.iters, a.warmup)
         print(f"{name} L={L} H={H}: {t:.3f} ms  {by / t / 1e6:.0f} GB/s")
+
+    # the whole pre-pass of one self-attention, both ways (algorithmic bytes: Q, K, V read once, 8-bit copies written)
+    def in_place():
+        m = ops.rmsnorm_rope_inplace(qkv[:, C:2 * C], w, 1e-6, rope, grid, want_mean=True)
+        ops.rmsnorm_rope_inplace(qkv[:, :C], w, 1e-6, rope, grid)
+        ops.sage_quant_int8(t3[:, 0], 128, premul=0.1)
+        ops.sage_quant_int8(t3[:, 1], 64, mean=m.view(H, 128))
+        ops.sage_quant_v(t3[:, 2])
+
+    def folded():
+        r = ops.rowsumsq_to_rstd(sums, C)
+        m = ops.sage_kmean_normed(t3[:, 1], w, 1e-6, rope, grid, row_rstd=r[1])
+        ops.sage_quant_int8_normed(t3[:, 0], 128, w, premul=0.1, rope=rope, grid=grid, row_rstd=r[0])
+        ops.sage_quant_int8_normed(t3[:, 1], 64, w, mean=m, rope=rope, grid=grid, row_rstd=r[1])
+        ops.sage_quant_v(t3[:, 2])
+
+    by = L * C * 9
+    for name, fn in (("pre-pass, norm + RoPE in place then quantise", in_place), ("pre-pass, norm + RoPE inside the quantisers", folded)):
+        t = timeit(fn, a.iters, a.warmup)
+        print(f"{name} L={L} H={H}: {t:.3f} ms  {by / t / 1e6:.0f} GB/s of algorithmic bytes")
 
 
 def run_qwen(a):

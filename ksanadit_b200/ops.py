@@ -272,6 +272,91 @@ def sage_quant_int8(x, block, premul=0.0, mean=None, out=None):
     return out, sc
 
 
+def fp8_gemm_rowstats(a_q, a_scale, w_q, w_scale, bias, sumsq_cols, out_dtype=torch.bfloat16, out=None):
+    """fp8_gemm without epilogue that also returns tile_sumsq [sumsq_cols / 256, M] fp32: per 256-column tile and row, the
+    sum of squares of the rounded outputs (the row statistics an RMSNorm over those columns needs)."""
+    _cuda(a_q, a_scale, w_q, w_scale, bias, out)
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    assert w_q.shape[1] == K and a_q.is_contiguous() and w_q.is_contiguous()
+    assert a_scale.dtype == torch.float32 and w_scale.dtype == torch.float32 and a_scale.numel() == M and w_scale.numel() == N
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    dt = _lib.BF16 if out.dtype == torch.bfloat16 else _lib.FP16
+    if bias is not None:
+        bias = bias.to(out.dtype).contiguous()
+    sums = torch.empty(sumsq_cols // 256, M, dtype=torch.float32, device=a_q.device)
+    STATS.timed(("gemm", M, N, K), lambda: _lib.check(
+        _lib.load().ksb_fp8_gemm_rowstats(_p(a_q), _p(a_scale), _p(w_q), _p(w_scale), _p(bias), M, N, K, _p(out), dt,
+                                          out.stride(0) if M > 1 else N, _p(sums), int(sumsq_cols), _stream()),
+        "ksb_fp8_gemm_rowstats"))
+    STATS.count(1)
+    return out, sums
+
+
+def rowsumsq_to_rstd(tile_sumsq, C, eps=1e-6):
+    """tile_sumsq [groups * C / 256, M] -> rstd [groups, M] = rsqrt(mean of squares over the C channels of a group + eps)."""
+    _cuda(tile_sumsq)
+    tiles, M = tile_sumsq.shape
+    assert tile_sumsq.dtype == torch.float32 and tile_sumsq.is_contiguous() and C % 256 == 0 and tiles % (C // 256) == 0
+    groups = tiles // (C // 256)
+    rstd = torch.empty(groups, M, dtype=torch.float32, device=tile_sumsq.device)
+    _lib.check(_lib.load().ksb_rowsumsq_to_rstd(_p(tile_sumsq), M, C, groups, float(eps), _p(rstd), _stream()), "ksb_rowsumsq_to_rstd")
+    STATS.count(1)
+    return rstd
+
+
+def _norm_args(x, w, eps, rope, grid, pos0, per_head, diag, row_rstd):
+    L, H = x.shape[0], x.shape[1]
+    _cuda(w, row_rstd)
+    assert w.dtype == torch.float32 and w.is_contiguous() and w.numel() == (128 if per_head else H * 128)
+    if not per_head:
+        assert row_rstd is not None and row_rstd.dtype == torch.float32 and row_rstd.is_contiguous() and row_rstd.numel() == L
+    tab, tlen, nf, nh, F, Hh, Ww = None, 0, 0, 0, 1, 1, 1
+    if rope is not None:
+        tab, nf, nh = rope
+        tlen = tab.shape[0]
+        F, Hh, Ww = (int(v) for v in grid)
+    return (_p(w), int(per_head), None if per_head else _p(row_rstd), float(eps), _p(tab), tlen, nf, nh, F, Hh, Ww, int(pos0), int(diag))
+
+
+def sage_kmean_normed(k, w, eps=1e-6, rope=None, grid=None, pos0=0, per_head=False, diag=False, row_rstd=None):
+    """Column means [H,128] of rope(rmsnorm(k)) for k [L,H,128], without writing the normalised tensor (the arguments
+    are those of rmsnorm_rope_inplace; row_rstd [L] is required unless per_head)."""
+    _cuda(k)
+    L, H, D, ts, hs = _lhd(k)
+    lib = _lib.load()
+    partial = torch.empty(lib.ksb_sage_kmean_scratch_floats(L, H, D), dtype=torch.float32, device=k.device)
+    km = torch.empty(H, D, dtype=torch.float32, device=k.device)
+    _lib.check(lib.ksb_sage_kmean_normed(_p(k), _dt(k), L, H, D, ts, hs, *_norm_args(k, w, eps, rope, grid, pos0, per_head, diag, row_rstd),
+                                         _p(partial), _p(km), _stream()), "ksb_sage_kmean_normed")
+    STATS.count(2)
+    return km
+
+
+def sage_quant_int8_normed(x, block, w, premul=0.0, mean=None, eps=1e-6, rope=None, grid=None, pos0=0, per_head=False, diag=False,
+                           row_rstd=None, out=None):
+    """sage_quant_int8 of rope(rmsnorm(x)) for x [L,H,128], reading x once and never writing the normalised tensor."""
+    _cuda(x, mean)
+    L, H, D, ts, hs = _lhd(x)
+    Lp = pad128(L)
+    if out is None:
+        out = torch.empty(H, Lp, D, dtype=torch.int8, device=x.device)
+        sc = torch.empty(H, Lp // block, dtype=torch.float32, device=x.device)
+    else:
+        out, sc = out
+        if out.shape != (H, Lp, D) or sc.shape != (H, Lp // block) or out.dtype != torch.int8 or sc.dtype != torch.float32 \
+                or not out.is_contiguous() or not sc.is_contiguous():
+            raise _lib.KsanaB200Error(f"out must be a contiguous ([{H}, {Lp}, {D}] int8, [{H}, {Lp // block}] float32) pair")
+        _cuda(out, sc)
+    _lib.check(_lib.load().ksb_sage_quant_int8_normed(_p(x), _dt(x), L, H, D, ts, hs, block, float(premul), _p(mean),
+                                                      *_norm_args(x, w, eps, rope, grid, pos0, per_head, diag, row_rstd),
+                                                      _p(out), _p(sc), _stream()), "ksb_sage_quant_int8_normed")
+    STATS.count(1)
+    return out, sc
+
+
 def sage_quant_v(v, out=None):
     """v [L,H,128] -> (vt [H,128,Lpad] float8_e4m3fn, vs [H,128]).  out: that pair, preallocated."""
     _cuda(v)

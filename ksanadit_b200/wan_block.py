@@ -163,12 +163,13 @@ class B200WanBlock(torch.nn.Module):
         Cl = Hl * HEAD
         La = ex.P * ex.L_loc
         w = slice(ex.rank * Cl, (ex.rank + 1) * Cl)
-        g = ex.qkv.view(La, 3, Cl)
-        km = ops.rmsnorm_rope_inplace(g[:, 1], sa.norm_k.weight[w], self.eps, rope, grid, want_mean=True, row_rstd=ex.rstd[1])
-        ops.rmsnorm_rope_inplace(g[:, 0], sa.norm_q.weight[w], self.eps, rope, grid, row_rstd=ex.rstd[0])
-        q3, k3, v3 = ex.qkv[:, 0], ex.qkv[:, 1], ex.qkv[:, 2]
-        q8, qs = ops.sage_quant_int8(q3, ops.Q_BLOCK, premul=ops.q_premul(HEAD))
-        k8, ks = ops.sage_quant_int8(k3, ops.K_BLOCK, mean=km.view(Hl, HEAD))
+        q3, k3, v3 = ex.qkv[:, 0], ex.qkv[:, 1], ex.qkv[:, 2]  # [La, Hl, 128] each
+        # norm + RoPE run inside the K mean and the quantisers, with the norm factors every rank stored in phase a
+        wq, wk = sa.norm_q.weight[w], sa.norm_k.weight[w]
+        km = ops.sage_kmean_normed(k3, wk, self.eps, rope, grid, row_rstd=ex.rstd[1])
+        q8, qs = ops.sage_quant_int8_normed(q3, ops.Q_BLOCK, wq, premul=ops.q_premul(HEAD), eps=self.eps, rope=rope, grid=grid,
+                                            row_rstd=ex.rstd[0])
+        k8, ks = ops.sage_quant_int8_normed(k3, ops.K_BLOCK, wk, mean=km, eps=self.eps, rope=rope, grid=grid, row_rstd=ex.rstd[1])
         vt, vs = ops.sage_quant_v(v3)
         offs, ents, order = self.tile_lists if self.tile_lists is not None else (None, None, None)
         esz = ex.out.element_size()
@@ -189,6 +190,20 @@ class B200WanBlock(torch.nn.Module):
             return ex.out.view(L, C)
         P, rank = distribute.get_world_size(), distribute.get_rank_id()
         sa = self.self_attn
+        if P == 1 and C % 256 == 0:
+            # one GPU: the norm factors come out of the projection's epilogue, and norm + RoPE run inside the K mean
+            # and the quantisers, so the normalised Q and K are never written (Q is read once, K twice)
+            qkv, sums = sa.qkv.forward_quantized_rowstats(xq, sx, self.dtype, 2 * C)
+            rstd = ops.rowsumsq_to_rstd(sums, C, self.eps)
+            t = qkv.view(L, 3, H, HEAD)
+            km = ops.sage_kmean_normed(t[:, 1], sa.norm_k.weight, self.eps, rope, grid, row_rstd=rstd[1])
+            q8, qs = ops.sage_quant_int8_normed(t[:, 0], ops.Q_BLOCK, sa.norm_q.weight, premul=ops.q_premul(HEAD), eps=self.eps,
+                                                rope=rope, grid=grid, row_rstd=rstd[0])
+            k8, ks = ops.sage_quant_int8_normed(t[:, 1], ops.K_BLOCK, sa.norm_k.weight, mean=km, eps=self.eps, rope=rope, grid=grid,
+                                                row_rstd=rstd[1])
+            vt, vs = ops.sage_quant_v(t[:, 2])
+            offs, ents, order = self.tile_lists if self.tile_lists is not None else (None, None, None)
+            return ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, self.dtype, offs, ents, tile_order=order).reshape(L, C)
         qkv = sa.qkv.forward_quantized(xq, sx, self.dtype)  # [L, 3C]
         km = ops.rmsnorm_rope_inplace(qkv[:, C:2 * C], sa.norm_k.weight, self.eps, rope, grid, pos0=rank * L, want_mean=(P == 1))
         ops.rmsnorm_rope_inplace(qkv[:, :C], sa.norm_q.weight, self.eps, rope, grid, pos0=rank * L)
@@ -226,10 +241,15 @@ class B200WanBlock(torch.nn.Module):
             hq, hs = ops.layernorm_quant_fp8(x, self.norm3.weight, self.norm3.bias, self.eps)
         else:
             hq, hs = ops.quant_fp8_rowwise(x)
-        q = ca.q.forward_quantized(hq, hs, self.dtype)
-        ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
         k8, ks, vt, vs, Lc = self._context_kv(context, ctx_owner, slot)
-        q8, qs = ops.sage_quant_int8(q.view(L, self.num_heads, HEAD), ops.Q_BLOCK, premul=ops.q_premul(HEAD))
+        if C % 256 == 0:
+            q, sums = ca.q.forward_quantized_rowstats(hq, hs, self.dtype, C)
+            q8, qs = ops.sage_quant_int8_normed(q.view(L, self.num_heads, HEAD), ops.Q_BLOCK, ca.norm_q.weight, premul=ops.q_premul(HEAD),
+                                                eps=self.eps, row_rstd=ops.rowsumsq_to_rstd(sums, C, self.eps)[0])
+        else:
+            q = ca.q.forward_quantized(hq, hs, self.dtype)
+            ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
+            q8, qs = ops.sage_quant_int8(q.view(L, self.num_heads, HEAD), ops.Q_BLOCK, premul=ops.q_premul(HEAD))
         o = ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, Lc, self.dtype).view(L, C)
         oq, os_ = ops.quant_fp8_rowwise(o)
         x = ca.o.forward_quantized(oq, os_, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=self._ones, out=x)
@@ -284,16 +304,33 @@ class B200WanBlock(torch.nn.Module):
 
         # ---- self-attention
         xq, sx = self._per_sample_quant(B, L, C, lambda b, out: ops.adaln_quant_fp8(x[b], e6[0][b:b + 1], e6[1][b:b + 1], self.eps, out=out))
-        qkv = sa.qkv.forward_quantized(xq, sx, self.dtype)  # [M, 3C]
         k8, ks, vt, vs = heads_operands(Lp)
+        folded = C % 256 == 0  # norm + RoPE inside the quantisers, as in _self_attention
+        if folded:
+            qkv, sums = sa.qkv.forward_quantized_rowstats(xq, sx, self.dtype, 2 * C)  # [M, 3C]
+            rstd = ops.rowsumsq_to_rstd(sums, C, self.eps)  # [2, M]
+            q8 = torch.empty(B * H, Lp, HEAD, dtype=torch.int8, device=dev)
+            qs = torch.empty(B * H, Lp // ops.Q_BLOCK, dtype=torch.float32, device=dev)
+        else:
+            qkv = sa.qkv.forward_quantized(xq, sx, self.dtype)
         for b in range(B):
             rows = qkv[b * L:(b + 1) * L]
-            km = ops.rmsnorm_rope_inplace(rows[:, C:2 * C], sa.norm_k.weight, self.eps, rope, grid, want_mean=True)
-            ops.rmsnorm_rope_inplace(rows[:, :C], sa.norm_q.weight, self.eps, rope, grid)
             t = rows.view(L, 3, H, HEAD)
-            ops.sage_quant_int8(t[:, 1], ops.K_BLOCK, mean=km.view(H, HEAD), out=(k8[b * H:(b + 1) * H], ks[b * H:(b + 1) * H]))
-            ops.sage_quant_v(t[:, 2], out=(vt[b * H:(b + 1) * H], vs[b * H:(b + 1) * H]))
-        q8, qs = quant_q(qkv[:, :C])
+            hb = slice(b * H, (b + 1) * H)
+            if folded:
+                rq, rk = rstd[0, b * L:(b + 1) * L], rstd[1, b * L:(b + 1) * L]
+                km = ops.sage_kmean_normed(t[:, 1], sa.norm_k.weight, self.eps, rope, grid, row_rstd=rk)
+                ops.sage_quant_int8_normed(t[:, 1], ops.K_BLOCK, sa.norm_k.weight, mean=km, eps=self.eps, rope=rope, grid=grid, row_rstd=rk,
+                                           out=(k8[hb], ks[hb]))
+                ops.sage_quant_int8_normed(t[:, 0], ops.Q_BLOCK, sa.norm_q.weight, premul=ops.q_premul(HEAD), eps=self.eps, rope=rope,
+                                           grid=grid, row_rstd=rq, out=(q8[hb], qs[hb]))
+            else:
+                km = ops.rmsnorm_rope_inplace(rows[:, C:2 * C], sa.norm_k.weight, self.eps, rope, grid, want_mean=True)
+                ops.rmsnorm_rope_inplace(rows[:, :C], sa.norm_q.weight, self.eps, rope, grid)
+                ops.sage_quant_int8(t[:, 1], ops.K_BLOCK, mean=km.view(H, HEAD), out=(k8[hb], ks[hb]))
+            ops.sage_quant_v(t[:, 2], out=(vt[hb], vs[hb]))
+        if not folded:
+            q8, qs = quant_q(qkv[:, :C])
         offs, ents, order = self.tile_lists if self.tile_lists is not None else (None, None, None)
         o = torch.empty(L, B, H, HEAD, dtype=self.dtype, device=dev)
         ops.sage_attn_core(q8, qs, k8, ks, vt, vs, L, L, self.dtype, offs, ents, out=o.view(L, B * H, HEAD), tile_order=order)
@@ -304,15 +341,24 @@ class B200WanBlock(torch.nn.Module):
             hq, hs = ops.layernorm_quant_fp8(x2, self.norm3.weight, self.norm3.bias, self.eps)
         else:
             hq, hs = ops.quant_fp8_rowwise(x2)
-        q = ca.q.forward_quantized(hq, hs, self.dtype)
-        ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
+        if folded:
+            q, sums = ca.q.forward_quantized_rowstats(hq, hs, self.dtype, C)
+            rstd = ops.rowsumsq_to_rstd(sums, C, self.eps)  # [1, M]
+        else:
+            q = ca.q.forward_quantized(hq, hs, self.dtype)
+            ops.rmsnorm_rope_inplace(q, ca.norm_q.weight, self.eps)
         Lc = context.shape[1]
         ck8, cks, cvt, cvs = heads_operands(ops.pad128(Lc))
         for b in range(B):
             kb, sb, vb, vsb, _ = self._context_kv(context[b], context, b)
             for dst, src in ((ck8, kb), (cks, sb), (cvt, vb), (cvs, vsb)):
                 dst[b * H:(b + 1) * H].copy_(src)
-        q8, qs = quant_q(q)
+        if folded:
+            for b in range(B):
+                ops.sage_quant_int8_normed(q[b * L:(b + 1) * L].view(L, H, HEAD), ops.Q_BLOCK, ca.norm_q.weight, premul=ops.q_premul(HEAD),
+                                           eps=self.eps, row_rstd=rstd[0, b * L:(b + 1) * L], out=(q8[b * H:(b + 1) * H], qs[b * H:(b + 1) * H]))
+        else:
+            q8, qs = quant_q(q)
         ops.sage_attn_core(q8, qs, ck8, cks, cvt, cvs, L, Lc, self.dtype, out=o.view(L, B * H, HEAD))
         oq, os_ = requant_attention_output(o)
         x2 = ca.o.forward_quantized(oq, os_, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x2, gate=self._ones, out=x2)
