@@ -386,24 +386,22 @@ struct NormSpec {
 
 constexpr int NQ_THREADS = 512;  // 32 token lanes x 16 column groups of 8 channels; 4 vectors per thread
 
-// Loads the thread's four vectors of tile (l0, h) and replaces them by the normalised (and rotated) values.
-template <typename T, bool PER_HEAD>
-__device__ __forceinline__ void load_normed_tile(const T* __restrict__ x, int64_t L, int64_t ts, int64_t hs, int h, int64_t l0,
-                                                 const NormSpec& ns, uint4 (&raw)[4]) {
+// Loads the thread's four vectors of tile (l0, h) and replaces them by the normalised (and rotated) values; rows
+// at or past nvalid (the tile's share of L) come back as zeros.  VIS(i, q, v) is called with every pair of final
+// values (as fp32, already rounded to half) of valid rows, while they are still in registers.
+template <typename T, bool PER_HEAD, typename Visitor>
+__device__ __forceinline__ void load_normed_tile(const T* __restrict__ x, int nvalid, int64_t ts, int64_t hs, int h, int64_t l0,
+                                                 const NormSpec& ns, uint4 (&raw)[4], Visitor&& vis) {
+  const int lane = threadIdx.x & 31;
   const int cg = threadIdx.x & 15, tl = threadIdx.x >> 4;
   const int c = cg * 8;
+  const T* xp = x + (l0 + tl) * ts + (int64_t)h * hs + c;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int64_t l = l0 + tl + 32 * i;
-    raw[i] = (l < L) ? *reinterpret_cast<const uint4*>(x + l * ts + (int64_t)h * hs + c) : make_uint4(0, 0, 0, 0);
-  }
+  for (int i = 0; i < 4; ++i) raw[i] = (tl + 32 * i < nvalid) ? *reinterpret_cast<const uint4*>(xp + 32 * i * ts) : make_uint4(0, 0, 0, 0);
   float rstd[4];
   if (!PER_HEAD) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int64_t l = l0 + tl + 32 * i;
-      rstd[i] = (l < L) ? ns.row_rstd[l] : 0.f;
-    }
+    for (int i = 0; i < 4; ++i) rstd[i] = (tl + 32 * i < nvalid) ? ns.row_rstd[l0 + tl + 32 * i] : 0.f;
   }
   float2 w2[4];
   {
@@ -411,10 +409,27 @@ __device__ __forceinline__ void load_normed_tile(const T* __restrict__ x, int64_
     const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
     w2[0] = make_float2(w0.x, w0.y); w2[1] = make_float2(w0.z, w0.w); w2[2] = make_float2(w1.x, w1.y); w2[3] = make_float2(w1.z, w1.w);
   }
+  // Grid coordinates of the four tokens: the 16 lanes that share a token would all decode the same position, so lane
+  // cg decodes the token of vector (cg & 3) and the group exchanges the results (packed 10 bits per axis; -1: the
+  // token lies past the grid and is not rotated).
   const int p0 = c >> 1;  // first of the four rotation pairs of these 8 channels
+  int packed = -1;
+  bool ax_f[4], ax_h[4];  // which axis drives pair p0 + q: fixed per thread
+  if (ns.rg.table) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      ax_f[q] = p0 + q < ns.rg.nf;
+      ax_h[q] = p0 + q < ns.rg.nf + ns.rg.nh;
+    }
+    const int pos = static_cast<int>(ns.rg.pos0 + l0) + tl + 32 * (cg & 3);
+    int cf, rem, ch, cw;
+    divmod_small(pos, ns.per_frame, ns.inv_per_frame, cf, rem);
+    divmod_small(rem, ns.rg.Ww, ns.inv_w, ch, cw);
+    if (ns.rg.diag) ch = cw = cf;
+    if (cf < ns.rg.F) packed = cf | (ch << 10) | (cw << 20);
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int64_t l = l0 + tl + 32 * i;
     const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);
     float2 f[4];
 #pragma unroll
@@ -433,32 +448,33 @@ __device__ __forceinline__ void load_normed_tile(const T* __restrict__ x, int64_
     } else {
       r = rstd[i];
     }
-    if (l >= L) continue;
+    int coords = -1;
+    if (ns.rg.table) coords = __shfl_sync(0xffffffffu, packed, (lane & 16) | i);  // uniform branch: every lane takes part
+    if (tl + 32 * i >= nvalid) continue;
     const float2 r2 = make_float2(r, r);
+    float2 y[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) y[q] = HalfOps<T>::unpack2(HalfOps<T>::pack2(__fmul2_rn(__fmul2_rn(f[q], r2), w2[q])));  // norm output, rounded to half
+    if (coords >= 0) {
+      const int cf = coords & 1023, ch = (coords >> 10) & 1023, cw = coords >> 20;
+      // pairs p0 .. p0+3 as two 16-byte table reads; a pair whose axis differs from its neighbour's is fetched on its own
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int pr = p0 + 2 * hf;
+        const int c0 = ax_f[2 * hf] ? cf : (ax_h[2 * hf] ? ch : cw);
+        const int c1 = ax_f[2 * hf + 1] ? cf : (ax_h[2 * hf + 1] ? ch : cw);
+        const float4 t4 = *reinterpret_cast<const float4*>(ns.rg.table + c0 * 64 + pr);
+        float2 cs1 = make_float2(t4.z, t4.w);
+        if (c1 != c0) cs1 = ns.rg.table[c1 * 64 + pr + 1];
+        y[2 * hf] = HalfOps<T>::unpack2(HalfOps<T>::pack2(rope_pair(y[2 * hf].x, y[2 * hf].y, make_float2(t4.x, t4.y))));
+        y[2 * hf + 1] = HalfOps<T>::unpack2(HalfOps<T>::pack2(rope_pair(y[2 * hf + 1].x, y[2 * hf + 1].y, cs1)));
+      }
+    }
     uint32_t nw[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) nw[q] = HalfOps<T>::pack2(__fmul2_rn(__fmul2_rn(f[q], r2), w2[q]));  // norm output, rounded to half
-    if (ns.rg.table) {
-      const int pos = static_cast<int>(ns.rg.pos0 + l);
-      int cf, rem, ch, cw;
-      divmod_small(pos, ns.per_frame, ns.inv_per_frame, cf, rem);
-      if (cf < ns.rg.F) {
-        divmod_small(rem, ns.rg.Ww, ns.inv_w, ch, cw);
-        if (ns.rg.diag) ch = cw = cf;
-        // pairs p0 .. p0+3 as two 16-byte table reads; a pair whose axis differs from its neighbour's is fetched on its own
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int pr = p0 + 2 * hf;
-          const int c0 = pr < ns.rg.nf ? cf : (pr < ns.rg.nf + ns.rg.nh ? ch : cw);
-          const int c1 = pr + 1 < ns.rg.nf ? cf : (pr + 1 < ns.rg.nf + ns.rg.nh ? ch : cw);
-          const float4 t4 = *reinterpret_cast<const float4*>(ns.rg.table + (int64_t)c0 * 64 + pr);
-          float2 cs0 = make_float2(t4.x, t4.y), cs1 = make_float2(t4.z, t4.w);
-          if (c1 != c0) cs1 = ns.rg.table[(int64_t)c1 * 64 + pr + 1];
-          const float2 y0 = HalfOps<T>::unpack2(nw[2 * hf]), y1 = HalfOps<T>::unpack2(nw[2 * hf + 1]);
-          nw[2 * hf] = HalfOps<T>::pack2(rope_pair(y0.x, y0.y, cs0));
-          nw[2 * hf + 1] = HalfOps<T>::pack2(rope_pair(y1.x, y1.y, cs1));
-        }
-      }
+    for (int q = 0; q < 4; ++q) {
+      nw[q] = HalfOps<T>::pack2(y[q]);  // exact: y is already rounded
+      vis(i, q, y[q]);
     }
     raw[i] = make_uint4(nw[0], nw[1], nw[2], nw[3]);
   }
@@ -477,14 +493,9 @@ __global__ void __launch_bounds__(NQ_THREADS, 2) normed_colsum_kernel(const T* _
   for (int tile = 0; tile < MEAN_CHUNK / 128; ++tile) {
     const int64_t l0 = (int64_t)chunk * MEAN_CHUNK + tile * 128;
     if (l0 >= L) break;
+    const int nvalid = (int)min((int64_t)128, L - l0);
     uint4 raw[4];
-    load_normed_tile<T, PER_HEAD>(x, L, ts, hs, h, l0, ns, raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);  // rows past L hold zeros
-#pragma unroll
-      for (int q = 0; q < 4; ++q) acc[q] = __fadd2_rn(acc[q], HalfOps<T>::unpack2(wd[q]));
-    }
+    load_normed_tile<T, PER_HEAD>(x, nvalid, ts, hs, h, l0, ns, raw, [&](int, int q, float2 v) { acc[q] = __fadd2_rn(acc[q], v); });
   }
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
@@ -509,16 +520,14 @@ __global__ void __launch_bounds__(NQ_THREADS, 2) normed_int8_quant_kernel(const 
   __shared__ float red[NB][NQ_THREADS / 32];
   const int h = blockIdx.y;
   const int64_t l0 = (int64_t)blockIdx.x * 128;
+  const int nvalid = (int)min((int64_t)128, L - l0);
   const int cg = threadIdx.x & 15, tl = threadIdx.x >> 4;
   const int c = cg * 8;
-  uint4 raw[4];
-  load_normed_tile<T, PER_HEAD>(x, L, ts, hs, h, l0, ns, raw);
   float2 nmu[4];  // minus the mean: x - mu and x + (-mu) are the same number
 #pragma unroll
   for (int q = 0; q < 4; ++q) nmu[q] = mean ? make_float2(-mean[h * D + c + 2 * q], -mean[h * D + c + 2 * q + 1]) : make_float2(0.f, 0.f);
   const float2 pm2 = make_float2(premul, premul);
-  auto value = [&](uint32_t wd, int q) -> float2 {
-    float2 v = HalfOps<T>::unpack2(wd);
+  auto value = [&](float2 v, int q) -> float2 {
     if (mean) v = __fadd2_rn(v, nmu[q]);
     if (premul != 0.f) v = __fmul2_rn(v, pm2);
     return v;
@@ -526,20 +535,12 @@ __global__ void __launch_bounds__(NQ_THREADS, 2) normed_int8_quant_kernel(const 
   float am[NB];
 #pragma unroll
   for (int b = 0; b < NB; ++b) am[b] = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (l0 + tl + 32 * i < L) {
-      const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);
-      float a = 0.f;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 v = value(wd[q], q);
-        a = fmax3(a, fabsf(v.x), fabsf(v.y));
-      }
-      const int b = NB == 2 ? (i >> 1) : 0;  // tokens tl + 32 i: i = 0, 1 are the first 64
-      am[b] = fmaxf(am[b], a);
-    }
-  }
+  uint4 raw[4];
+  load_normed_tile<T, PER_HEAD>(x, nvalid, ts, hs, h, l0, ns, raw, [&](int i, int q, float2 y) {
+    const float2 v = value(y, q);
+    const int b = NB == 2 ? (i >> 1) : 0;  // tokens tl + 32 i: i = 0, 1 are the first 64
+    am[b] = fmax3(am[b], fabsf(v.x), fabsf(v.y));
+  });
 #pragma unroll
   for (int b = 0; b < NB; ++b) {
     am[b] = warp_max(am[b]);
@@ -556,16 +557,16 @@ __global__ void __launch_bounds__(NQ_THREADS, 2) normed_int8_quant_kernel(const 
     if (threadIdx.x == 0) scale[(int64_t)h * (Lpad / 128 * NB) + (int64_t)blockIdx.x * NB + b] = (a > 0.f) ? __fdiv_rn(a, 127.f) : 1.f;
   }
   // rounding by the magic addend: see int8_block_quant_kernel
+  int8_t* op = out + ((int64_t)h * Lpad + l0 + tl) * D + c;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int r = tl + 32 * i;
     const uint32_t* wd = reinterpret_cast<const uint32_t*>(&raw[i]);
     const float iv = inv[NB == 2 ? (i >> 1) : 0];
     uint32_t t[8];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float2 v = make_float2(0.f, 0.f);  // padding rows quantise to 0 whatever the mean
-      if (l0 + r < L) v = value(wd[q], q);
+      if (tl + 32 * i < nvalid) v = value(HalfOps<T>::unpack2(wd[q]), q);
       // scalar on purpose: the product must be rounded before the addition (a packed multiply followed by a packed
       // add was observed to round like one fused operation, which breaks ties such as 63.5 the other way)
       t[2 * q] = __float_as_uint(__fadd_rn(__fmul_rn(v.x, iv), 12582912.f));
@@ -575,7 +576,7 @@ __global__ void __launch_bounds__(NQ_THREADS, 2) normed_int8_quant_kernel(const 
 #pragma unroll
     for (int g = 0; g < 2; ++g)
       w[g] = __byte_perm(__byte_perm(t[4 * g], t[4 * g + 1], 0x0040), __byte_perm(t[4 * g + 2], t[4 * g + 3], 0x0040), 0x5410);
-    *reinterpret_cast<uint2*>(out + ((int64_t)h * Lpad + l0 + r) * D + c) = make_uint2(w[0], w[1]);
+    *reinterpret_cast<uint2*>(op + 32 * i * D) = make_uint2(w[0], w[1]);
   }
 }
 
