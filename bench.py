@@ -198,16 +198,17 @@ def secondary_measurements(dev):
     txt = torch.randn(1, Lt, dim, device=dev).to(torch.bfloat16)
     temb = torch.randn(1, dim, device=dev).to(torch.bfloat16)
 
+    from ksanadit_b200.qwen_block import B200QwenDenoiseStep
+    qdriver = B200QwenDenoiseStep(blocks)  # modulation rows ahead of the loop, text stream beside the image stream
+
     def qstep():
-        t_, i_ = txt, img
-        for b in blocks:
-            t_, i_ = b(i_, t_, temb, img_grid=grid)
-        return i_
+        return qdriver(img, txt, temb, img_grid=grid)[1]
 
     Lj = Li + Lt
     qfl = layers * (2.0 * Lj * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * Lj * Lj * 128)
     tq = _median_ms(qstep, iters=5, warmup=2)
     out["config4_qwen_image_step"] = {"blocks": layers, "dim": dim, "heads": heads, "image_tokens": Li, "text_tokens": Lt, "ms": tq,
+                                      "driver": "B200QwenDenoiseStep (eager launches, text stream on a second CUDA stream)",
                                       "tflops": qfl / tq / 1e9, "step_pflop": qfl / 1e15}
     del blocks
     torch.cuda.empty_cache()

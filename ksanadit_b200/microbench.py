@@ -186,20 +186,25 @@ def run_qwen(a):
         return
     fl = layers * (2.0 * L * (3 * dim * dim + dim * dim + 2 * dim * ffn) + 2.0 * 2 * dim * 6 * dim + 4.0 * heads * L * L * 128)
     t = timeit(step, a.iters, a.warmup)
-    print(f"qwen-image step, eager launches: {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s ({fl / 1e15:.4f} PFLOP)")
+    print(f"qwen-image step, block after block: {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s ({fl / 1e15:.4f} PFLOP)")
     from .graph import StepGraph
-
-    def blocks_fn(i, t_, e):
-        for b in blocks:
-            t_, i = b(i, t_, e, img_grid=grid)
-        return i
-
-    g = StepGraph(blocks_fn, (img, txt, temb))
+    from .qwen_block import B200QwenDenoiseStep
     ref = step().float()
-    got = g(img, txt, temb).float()
-    print("  graph replay equals eager:", bool((ref == got).all()), f"({g.kernels_per_replay} kernels per replay)")
-    t = timeit(lambda: g(img, txt, temb), a.iters, a.warmup)
-    print(f"qwen-image step, one CUDA graph:  {layers} blocks, {Li}+{Lt} tokens: {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s")
+    for text_stream in (False, True):
+        drv = B200QwenDenoiseStep(blocks, text_stream=text_stream)
+
+        def run(i=img, t_=txt, e=temb):
+            with torch.no_grad():
+                return drv(i, t_, e, img_grid=grid)[1]
+
+        tag = "modulations ahead" + (" + text stream" if text_stream else "")
+        got = run().float()
+        t = timeit(run, a.iters, a.warmup)
+        print(f"qwen-image step driver ({tag}): {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s  equals the plain loop: {bool((ref == got).all())}")
+        g = StepGraph(lambda i, t_, e: drv(i, t_, e, img_grid=grid)[1], (img, txt, temb))
+        got = g(img, txt, temb).float()
+        t = timeit(lambda: g(img, txt, temb), a.iters, a.warmup)
+        print(f"  as one CUDA graph ({g.kernels_per_replay} kernels per replay): {t:.2f} ms  {fl / t / 1e9:.1f} TFLOP/s  equals: {bool((ref == got).all())}")
 
 
 def main():

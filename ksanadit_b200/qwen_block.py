@@ -129,10 +129,12 @@ class B200QwenBlock(torch.nn.Module):
             self._rotary_tables = (key, tabs[0], tabs[1])
         return (self._rotary_tables[1], 0, 0), (self._rotary_tables[2], 0, 0)
 
-    def _modulation(self, st):
+    def _modulation(self, st, quantized=None, out=None):
         """img_mod and txt_mod (transformer.py:204-211) as ONE GEMM: both are Linears of the same one-row input, and at
         one row a GEMM only streams its weight, so two launches cost twice the fixed part.  The two weights are
-        concatenated once; the modules' own parameters become views of the concatenation (no second copy)."""
+        concatenated once; the modules' own parameters become views of the concatenation (no second copy).
+        ``quantized``: (xq, sx) of ``st`` when the caller has quantised it already (the same rows feed every block);
+        ``out``: a [rows, 12 C] buffer to write."""
         im, tm = self.img_mod[1], self.txt_mod[1]
         key = (im.weight.data_ptr(), tm.weight.data_ptr(), im.scale_weight.data_ptr(), tm.scale_weight.data_ptr())
         if self._mod_fused is None or self._mod_fused[0] != key:
@@ -144,8 +146,8 @@ class B200QwenBlock(torch.nn.Module):
             key = (im.weight.data_ptr(), tm.weight.data_ptr(), im.scale_weight.data_ptr(), tm.scale_weight.data_ptr())
             self._mod_fused = (key, w, sc, b)
         _, w, sc, b = self._mod_fused
-        xq, sx = ops.quant_fp8_rowwise(st)
-        return ops.fp8_gemm(xq, sx, w, sc, b, out_dtype=self.dtype)
+        xq, sx = quantized if quantized is not None else ops.quant_fp8_rowwise(st)
+        return ops.fp8_gemm(xq, sx, w, sc, b, out_dtype=self.dtype, out=out)
 
     def _stream_tail(self, x, attn_out, gate1, mod2, out_lin, mlp):
         """x + gate1 * out(attn_out), then x + gate2 * mlp(modulate(LN(x)))  (transformer.py:225-234)."""
@@ -157,7 +159,8 @@ class B200QwenBlock(torch.nn.Module):
         hq, hs = ops.quant_fp8_rowwise(h)
         return mlp.net[2].forward_quantized(hq, hs, self.dtype, _lib.EPI_GATE_RESIDUAL, resid=x, gate=gate2, out=x)
 
-    def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, img_grid=None, modulate_index=None, **_):
+    def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, img_grid=None, modulate_index=None, mods=None,
+                side_stream=None, **_):
         """hidden_states [1, Li, C] (image; under sequence parallelism this rank's Li rows of the P * Li image
         tokens, rows past the grid being padding), encoder_hidden_states [1, Lt, C] (text, replicated),
         temb [1, C]; img_grid (F, H, W) of all image tokens.  Returns (text, image) like the reference block.
@@ -166,7 +169,11 @@ class B200QwenBlock(torch.nn.Module):
 
         ``zero_cond_t`` blocks (transformer.py:171-188,206-208) take temb [2, C] = [real timestep; zero timestep]
         and ``modulate_index`` [1, Li] in {0, 1}: every image token reads its shift / scale / gate from the row
-        its index names (the kernels take one modulation row per token), the text stream uses row 0."""
+        its index names (the kernels take one modulation row per token), the text stream uses row 0.
+
+        ``mods``: this block's modulation rows [rows, 12 C] when the caller has computed them ahead (``B200QwenDenoiseStep``).
+        ``side_stream``: a CUDA stream for the text stream's kernels (one GPU only): its few-tile GEMMs and row passes
+        then fill the idle SMs at the ends of the image stream's launches instead of running alone."""
         if hidden_states.shape[0] != 1:
             raise _lib.KsanaB200Error("batch 1 only")
         if img_grid is None and image_rotary_emb is None:
@@ -187,10 +194,12 @@ class B200QwenBlock(torch.nn.Module):
             if img_tab[0].shape[0] < P * Li or txt_tab[0].shape[0] < Lt:
                 raise _lib.KsanaB200Error("image_rotary_emb is shorter than the token sequences")
             img_rope = ((img_tab[0].shape[0], 1, 1), True)
-        st = torch.nn.functional.silu(temb)
-        if st.shape[0] != (2 if self.zero_cond_t else 1) or (modulate_index is not None) != self.zero_cond_t:
+        if temb.shape[0] != (2 if self.zero_cond_t else 1) or (modulate_index is not None) != self.zero_cond_t:
             raise _lib.KsanaB200Error("a zero_cond_t block takes temb [2, C] and a modulate_index; any other block temb [1, C] and none")
-        mods = self._modulation(st)  # [rows, 12 C]: image then text, each [mod1|mod2] x [shift|scale|gate]
+        if mods is None:
+            mods = self._modulation(torch.nn.functional.silu(temb))  # [rows, 12 C]: image then text, each [mod1|mod2] x [shift|scale|gate]
+        elif mods.shape != (temb.shape[0], 12 * C):
+            raise _lib.KsanaB200Error(f"mods must be [{temb.shape[0]}, {12 * C}]")
         if self.zero_cond_t:
             index = modulate_index.reshape(-1).to(img.device, torch.int64)
             if index.numel() != Li:
@@ -203,14 +212,36 @@ class B200QwenBlock(torch.nn.Module):
         # local projections: text rows first (attention.py:355-357), then this rank's image rows
         qkv = torch.empty(Lt + Li, 3 * C, dtype=self.dtype, device=img.device)
         a = self.attn
-        for x, mod, lin, nq, nk, rows, tab, grid, diag, pos0 in (
-            (txt, tmod, a.add_qkv_proj, "norm_added_q", "norm_added_k", slice(0, Lt), txt_tab, (txt_tab[0].shape[0] if img_grid is None else Lt, 1, 1), True, 0),
-            (img, imod, a.to_qkv, "norm_q", "norm_k", slice(Lt, Lt + Li), img_tab, img_rope[0], img_rope[1], rank * Li),
-        ):
+        main = torch.cuda.current_stream()
+        side = side_stream if (side_stream is not None and P == 1) else None
+
+        def on_text_stream(fn, after):
+            """Runs fn on the text stream once ``after`` (an event of the main stream) has passed; returns its result and
+            the event that marks its end.  Without a text stream fn simply runs here."""
+            if side is None:
+                return fn(), None
+            with torch.cuda.stream(side):
+                side.wait_event(after)
+                r = fn()
+                done = torch.cuda.Event()
+                done.record(side)
+            return r, done
+
+        def project(x, mod, lin, nq, nk, rows, tab, grid, diag, pos0):
             xq, sx = ops.adaln_quant_fp8(x, mod[0, 0], mod[0, 1], self.eps, round_product=True)
             lin.forward_quantized(xq, sx, self.dtype, out=qkv[rows])
             ops.rmsnorm_rope_inplace(qkv[rows, :C], self._norm_weight(nq), self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
             ops.rmsnorm_rope_inplace(qkv[rows, C:2 * C], self._norm_weight(nk), self.eps, tab, grid, per_head=True, diag=diag, pos0=pos0)
+
+        start = None
+        if side is not None:
+            start = torch.cuda.Event()
+            start.record(main)  # qkv, mods and both inputs are ready (in stream order) from here on
+        _, txt_projected = on_text_stream(lambda: project(txt, tmod, a.add_qkv_proj, "norm_added_q", "norm_added_k", slice(0, Lt), txt_tab,
+                                                          (txt_tab[0].shape[0] if img_grid is None else Lt, 1, 1), True, 0), start)
+        project(img, imod, a.to_qkv, "norm_q", "norm_k", slice(Lt, Lt + Li), img_tab, img_rope[0], img_rope[1], rank * Li)
+        if txt_projected is not None:
+            main.wait_event(txt_projected)
         if P == 1:
             t = qkv.view(Lt + Li, 3, H, HEAD)
             o = ops.sage_attention(t[:, 0], t[:, 1], t[:, 2]).view(Lt + Li, C)
@@ -223,8 +254,66 @@ class B200QwenBlock(torch.nn.Module):
             o = ops.sage_attention(joint[:, 0], joint[:, 1], joint[:, 2])  # [Lt + P*Li, Hl, D]
             o_txt = distribute.gather_heads(o[:Lt]).reshape(Lt, C)
             o_img = distribute.sequence_to_heads(o[Lt:]).reshape(Li, C)
-        txt = self._stream_tail(txt, o_txt, tmod[0, 2], tmod[1], a.to_add_out, self.txt_mlp)
+        attended = None
+        if side is not None:
+            attended = torch.cuda.Event()
+            attended.record(main)
+        txt, txt_done = on_text_stream(lambda: self._stream_tail(txt, o_txt, tmod[0, 2], tmod[1], a.to_add_out, self.txt_mlp), attended)
         img = self._stream_tail(img, o_img, imod[0, 2], imod[1], a.to_out[0], self.img_mlp)
+        if txt_done is not None:
+            main.wait_event(txt_done)  # everything this block launched is ordered before whatever follows on this stream
         if self.dtype == torch.float16:  # transformer.py:236-239: an overflow to inf comes back as the largest fp16
             txt, img = txt.clamp_(-65504, 65504), img.clamp_(-65504, 65504)
         return txt.unsqueeze(0), img.unsqueeze(0)
+
+
+class B200QwenDenoiseStep(torch.nn.Module):
+    """The per-step loop over the dual-stream blocks (``for block in self.transformer_blocks``,
+    ksana/models/qwen/transformer.py:196-241 called once per block) with the two things a block cannot do on its own:
+
+    * every block's modulation rows depend on the timestep embedding only, and computing them streams 12 C x C weights
+      per block through a one-row GEMM: they are all launched at the start of the step on a stream of their own, so
+      the weight streaming hides under the first blocks' tensor-core work;
+    * ``text_stream=True`` (one GPU): the text stream's kernels of every block run on a second stream beside the image
+      stream's (see ``B200QwenBlock.forward``).
+
+    The caller's stream waits for both before this returns, and the step can be captured into a CUDA graph."""
+
+    def __init__(self, blocks, text_stream=True):
+        super().__init__()
+        self.blocks = torch.nn.ModuleList(blocks)
+        self.text_stream = text_stream
+        self._streams = None
+
+    def _side_streams(self, device):
+        if self._streams is None or self._streams[0].device != device:
+            self._streams = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+        return self._streams
+
+    def forward(self, hidden_states, encoder_hidden_states, temb, img_grid=None, image_rotary_emb=None, modulate_index=None):
+        img, txt = hidden_states, encoder_hidden_states
+        main = torch.cuda.current_stream()
+        mod_stream, txt_stream = self._side_streams(img.device)
+        b0 = self.blocks[0]
+        C = b0.dim
+        st = torch.nn.functional.silu(temb)
+        quantized = ops.quant_fp8_rowwise(st)
+        mods = torch.empty(len(self.blocks), temb.shape[0], 12 * C, dtype=b0.dtype, device=img.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        events = []
+        with torch.cuda.stream(mod_stream):
+            mod_stream.wait_event(ready)
+            for i, blk in enumerate(self.blocks):
+                blk._modulation(st, quantized=quantized, out=mods[i])
+                ev = torch.cuda.Event()
+                ev.record(mod_stream)
+                events.append(ev)
+        side = txt_stream if (self.text_stream and distribute.get_world_size() == 1) else None
+        for i, blk in enumerate(self.blocks):
+            main.wait_event(events[i])
+            txt, img = blk(img, txt, temb, image_rotary_emb=image_rotary_emb, img_grid=img_grid, modulate_index=modulate_index,
+                           mods=mods[i], side_stream=side)
+        if side is not None:
+            txt.record_stream(main)  # allocated on the text stream, handed to the caller's stream
+        return txt, img

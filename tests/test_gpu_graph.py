@@ -52,6 +52,46 @@ def test_qwen_block_graph_replay_equals_eager():
     assert torch.equal(ref, got)
 
 
+@pytest.mark.parametrize("text_stream", [False, True])
+def test_qwen_step_driver_equals_the_block_loop(text_stream):
+    """B200QwenDenoiseStep launches every block's modulation GEMM ahead on a stream of its own and (optionally) the text
+    stream's kernels beside the image stream's: same bits as calling the blocks one after the other, eagerly and as one
+    CUDA graph on new inputs."""
+    from ksanadit_b200 import _lib
+    from ksanadit_b200.graph import StepGraph
+    from ksanadit_b200.qwen_block import B200QwenBlock, B200QwenDenoiseStep
+    dim, heads, ffn, grid, Lt = 512, 4, 1024, (1, 8, 12), 40
+    Li = grid[1] * grid[2]
+    blocks = [B200QwenBlock(dim, heads, ffn).random_init(20 + i) for i in range(3)]
+    drv = B200QwenDenoiseStep(blocks, text_stream=text_stream)
+    g = torch.Generator().manual_seed(6)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).cuda()
+
+    def loop(i, t, e):
+        for b in blocks:
+            t, i = b(i, t, e, img_grid=grid)
+        return torch.cat([t, i], dim=1)
+
+    def driven(i, t, e):
+        t2, i2 = drv(i, t, e, img_grid=grid)
+        return torch.cat([t2, i2], dim=1)
+
+    img, txt, temb = mk(1, Li, dim), mk(1, Lt, dim), mk(1, dim)
+    with torch.no_grad():
+        ref = loop(img, txt, temb)
+        got = driven(img, txt, temb)
+    torch.cuda.synchronize()
+    _lib.assert_device_ok()
+    assert torch.equal(ref, got)
+    graph = StepGraph(driven, (img, txt, temb))
+    img2, txt2, temb2 = mk(1, Li, dim), mk(1, Lt, dim), mk(1, dim)
+    with torch.no_grad():
+        ref2 = loop(img2, txt2, temb2).clone()
+    got2 = graph(img2, txt2, temb2).clone()
+    _lib.assert_device_ok()
+    assert torch.equal(ref2, got2)
+
+
 def test_step_graph_rejects_other_shapes():
     from ksanadit_b200 import _lib
     from ksanadit_b200.graph import StepGraph
