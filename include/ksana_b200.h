@@ -187,6 +187,13 @@ int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t 
                         int64_t head_stride, int block, float premul, const float* mean, void* out,
                         float* scale, ksb_stream_t stream);
 
+/* How ksb_fp8_gemm (and _rowstats) drive the tensor cores: 0 = every CTA computes 128 x 256 tiles on its own
+ * (tcgen05.mma.cta_group::1); 1 = two CTAs of a cluster share 256 x 256 tiles (cta_group::2), each fetching its own half
+ * of the operands (the default; both forms give the same bits).  Sets the mode when `mode` is 0 or 1, leaves it
+ * otherwise (pass -1 to query); returns the mode that was in force before the call.  Process-wide;
+ * ksb_fp8_gemm_qkv_scatter always uses the single-CTA form. */
+int ksb_gemm_pair_mode(int mode);
+
 /* The QKV projection with row statistics: ksb_fp8_gemm with KSB_EPI_NONE that also writes, for every 256-column
  * tile that starts below column sumsq_cols (a multiple of 256) and every row m, the sum of squares of the rounded
  * outputs of that tile to tile_sumsq[tile_n][m] (fp32 [sumsq_cols / 256, M]).  RMSNorm over the C leading channels
@@ -242,7 +249,6 @@ int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H,
  * Replaces `sageattn(q, k, v, tensor_layout="NHD")` (sage_attn.py:75-81) and
  * `block_sparse_sage2_attn_cuda(q, k, v, mask_id=...)` (radial_sage_attn/radial_sage_attn.py:170-176).
  *   q8 [H,Lq_pad,128], qs [H,Lq_pad/128], k8 [H,Lk_pad,128], ks [H,Lk_pad/64], vt [H,128,Lk_pad], vs [H,128]
- *   (ks 8-byte aligned: the two 64-key scales of a 128-key tile are read as one pair)
  *   out[l,h,:] (half, element strides out_token_stride / out_head_stride) for l < Lq.
  * Block-sparse: tile_offsets int32 [Lq_pad/128 + 1] and tile_entries int32 [nnz] (shared by all heads);
  * entry = kv_tile*4 + keep bits (bit0: tokens 0-63 of the 128-token tile, bit1: tokens 64-127), ascending

@@ -48,6 +48,7 @@ SIGNATURES = {
     "ksb_fp8_gemm_qkv_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                          c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p]),
     "ksb_rowsumsq_to_rstd_scatter": (c_int, [c_void_p, c_int64, c_int64, c_float, c_void_p, c_int, c_int, c_void_p]),
+    "ksb_gemm_pair_mode": (c_int, [c_int]),
     "ksb_fp8_gemm_rowstats": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int,
                                       c_int64, c_void_p, c_int64, c_void_p]),
     "ksb_rowsumsq_to_rstd": (c_int, [c_void_p, c_int64, c_int64, c_int, c_float, c_void_p, c_void_p]),

@@ -191,6 +191,62 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA pairs (a cluster of two CTAs driving one tcgen05.mma.cta_group::2): each CTA holds its 128 rows of A, its half
+// of the B tile and its 128 accumulator rows; the even CTA of the pair issues the MMAs for both.  None of the loads
+// is shared between CTAs: every CTA fetches its own operands into its own shared memory, and only the completion
+// signals cross over.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address of this CTA's shared-memory location `addr` as CTA `rank` of the cluster holds it
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// tiled load into this CTA's shared memory whose completion is counted by an mbarrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs, 256 rows] (+)= A[128 rows in each CTA] * B[half the columns in each CTA]; e4m3 -> f32
+__device__ __forceinline__ void mma_f8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the mbarrier at this offset in both CTAs of the pair once every MMA issued so far has completed.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+               : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base_lane + i).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -201,35 +257,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-// 32 lanes x 64 consecutive 32-bit columns in one instruction, into chunks HALF*2 and HALF*2+1 of r
-// (r[c][i] = column 32 c + i of the 128-column block that starts 64 * HALF columns before taddr).
-template <int HALF>
-__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[4][32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-      " %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-      " %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-      : "=r"(r[2 * HALF + 0][0]), "=r"(r[2 * HALF + 0][1]), "=r"(r[2 * HALF + 0][2]), "=r"(r[2 * HALF + 0][3]),
-        "=r"(r[2 * HALF + 0][4]), "=r"(r[2 * HALF + 0][5]), "=r"(r[2 * HALF + 0][6]), "=r"(r[2 * HALF + 0][7]),
-        "=r"(r[2 * HALF + 0][8]), "=r"(r[2 * HALF + 0][9]), "=r"(r[2 * HALF + 0][10]), "=r"(r[2 * HALF + 0][11]),
-        "=r"(r[2 * HALF + 0][12]), "=r"(r[2 * HALF + 0][13]), "=r"(r[2 * HALF + 0][14]), "=r"(r[2 * HALF + 0][15]),
-        "=r"(r[2 * HALF + 0][16]), "=r"(r[2 * HALF + 0][17]), "=r"(r[2 * HALF + 0][18]), "=r"(r[2 * HALF + 0][19]),
-        "=r"(r[2 * HALF + 0][20]), "=r"(r[2 * HALF + 0][21]), "=r"(r[2 * HALF + 0][22]), "=r"(r[2 * HALF + 0][23]),
-        "=r"(r[2 * HALF + 0][24]), "=r"(r[2 * HALF + 0][25]), "=r"(r[2 * HALF + 0][26]), "=r"(r[2 * HALF + 0][27]),
-        "=r"(r[2 * HALF + 0][28]), "=r"(r[2 * HALF + 0][29]), "=r"(r[2 * HALF + 0][30]), "=r"(r[2 * HALF + 0][31]),
-        "=r"(r[2 * HALF + 1][0]), "=r"(r[2 * HALF + 1][1]), "=r"(r[2 * HALF + 1][2]), "=r"(r[2 * HALF + 1][3]),
-        "=r"(r[2 * HALF + 1][4]), "=r"(r[2 * HALF + 1][5]), "=r"(r[2 * HALF + 1][6]), "=r"(r[2 * HALF + 1][7]),
-        "=r"(r[2 * HALF + 1][8]), "=r"(r[2 * HALF + 1][9]), "=r"(r[2 * HALF + 1][10]), "=r"(r[2 * HALF + 1][11]),
-        "=r"(r[2 * HALF + 1][12]), "=r"(r[2 * HALF + 1][13]), "=r"(r[2 * HALF + 1][14]), "=r"(r[2 * HALF + 1][15]),
-        "=r"(r[2 * HALF + 1][16]), "=r"(r[2 * HALF + 1][17]), "=r"(r[2 * HALF + 1][18]), "=r"(r[2 * HALF + 1][19]),
-        "=r"(r[2 * HALF + 1][20]), "=r"(r[2 * HALF + 1][21]), "=r"(r[2 * HALF + 1][22]), "=r"(r[2 * HALF + 1][23]),
-        "=r"(r[2 * HALF + 1][24]), "=r"(r[2 * HALF + 1][25]), "=r"(r[2 * HALF + 1][26]), "=r"(r[2 * HALF + 1][27]),
-        "=r"(r[2 * HALF + 1][28]), "=r"(r[2 * HALF + 1][29]), "=r"(r[2 * HALF + 1][30]), "=r"(r[2 * HALF + 1][31])
       : "r"(taddr)
       : "memory");
 }

@@ -27,16 +27,25 @@ namespace gemm {
 
 constexpr int BM = 128, BN = 256, BK = 128;  // BK in bytes == e4m3 elements
 constexpr int UMMA_K = 32;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int A_BYTES = BM * BK;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID = 1;
 // Output staging of the scatter epilogue: one 128-byte row piece per epilogue thread, rows 144 bytes apart (the
 // 16-byte skew keeps the 16-byte shared-memory stores of a quarter warp on distinct banks).
 constexpr int SCATTER_COLS = 64, SCATTER_ROW_BYTES = SCATTER_COLS * 2 + 16, SCATTER_BYTES = 128 * SCATTER_ROW_BYTES;
-// dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers][scatter staging]
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256 + SCATTER_BYTES;
+// CTAS = 1: every CTA computes 128 x 256 tiles on its own.  CTAS = 2: two CTAs of a cluster compute one 256 x 256
+// tile with tcgen05.mma.cta_group::2 -- each holds its 128 rows of A and 128 of the 256 rows of the W tile, so a
+// stage is 32 KB instead of 48 KB per CTA (a third less operand traffic from L2 and into shared memory per flop)
+// and six stages fit where four did.
+template <int CTAS> struct Cfg {
+  static constexpr int B_ROWS = BN / CTAS;
+  static constexpr int B_BYTES = B_ROWS * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = CTAS == 1 ? 4 : 6;
+  // dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers][scatter staging]
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256 + SCATTER_BYTES;
+};
 
 struct Params {
   int M, N, K;
@@ -90,9 +99,10 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return __fdividef(x, 1.f + __expf(-2.f * u));
 }
 
-template <typename T>
+template <typename T, int CTAS>
 __global__ void __launch_bounds__(THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const Params p) {
+  constexpr int STAGES = Cfg<CTAS>::STAGES, STAGE_BYTES = Cfg<CTAS>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -103,27 +113,36 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + STAGES * STAGE_BYTES + 3 * BN * 4 + 16 * STAGES + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  // A pair walks the 256-row tiles together; CTA `crank` of the pair owns rows crank * 128 .. + 127 of each.
+  const uint32_t crank = CTAS == 2 ? cluster_ctarank() : 0u;
+  const int worker = CTAS == 2 ? blockIdx.x >> 1 : blockIdx.x, workers = CTAS == 2 ? gridDim.x >> 1 : gridDim.x;
+  const int tiles_m = (p.M + CTAS * BM - 1) / (CTAS * BM), tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_k = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, 1);
+      mbar_init(full0 + 8 * s, 1);   // the producer's expect_tx arrival (of the even CTA in a pair) + the bytes of every load
+      mbar_init(empty0 + 8 * s, 1);  // one commit (delivered to both CTAs of a pair)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
-      mbar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
+      mbar_init(tempty0 + 8 * a, 4 * CTAS);  // one arrival per epilogue warp (of both CTAs, at the even CTA)
     }
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (CTAS == 2) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // the partner's barriers exist before anything is signalled to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
 
@@ -134,26 +153,34 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       tma_prefetch_desc(&tmap_w);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < num_tiles && ok; tile += workers) {
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
         for (int k = 0; k < num_k; ++k, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, p.status, (KERNEL_ID << 16) | 1)) { ok = false; break; }
           const uint32_t sa = base + s * STAGE_BYTES;
-          mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, full0 + 8 * s, k * BK, tm * BM);
-          tma_load_2d(sa + A_BYTES, &tmap_w, full0 + 8 * s, k * BK, tn * BN);
+          if (CTAS == 2) {
+            // both CTAs' loads of this stage are counted by the even CTA's barrier, whose MMA thread consumes them
+            const uint32_t full_even = mapa_shared(full0 + 8 * s, 0);
+            if (crank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+            tma_load_2d_pair(sa, &tmap_a, full_even, k * BK, (tm * 2 + (int)crank) * BM);
+            tma_load_2d_pair(sa + A_BYTES, &tmap_w, full_even, k * BK, tn * BN + (int)crank * Cfg<CTAS>::B_ROWS);
+          } else {
+            mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_2d(sa, &tmap_a, full0 + 8 * s, k * BK, tm * BM);
+            tma_load_2d(sa + A_BYTES, &tmap_w, full0 + 8 * s, k * BK, tn * BN);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = IDESC_F8_E4M3_F32(BM, BN);
+    // ------------------------------------------------------------------ MMA issuer (in a pair: the even CTA's)
+    if (lane == 0 && crank == 0) {
+      constexpr uint32_t idesc = IDESC_F8_E4M3_F32(CTAS * BM, BN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = worker; tile < num_tiles && ok; tile += workers, ++tcount) {
         const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
         if (!mbar_wait(tempty0 + 8 * acc, aph ^ 1, p.status, (KERNEL_ID << 16) | 2)) { ok = false; break; }
         tc_fence_after();
@@ -165,11 +192,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t sa = base + s * STAGE_BYTES;
           const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + A_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            mma_f8_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0);
-          mma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            if (CTAS == 2) mma_f8_ss_pair(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0);
+            else mma_f8_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0);
+          }
+          // frees the stage (in both CTAs) once these MMAs have read it
+          if (CTAS == 2) mma_commit_pair(empty0 + 8 * s); else mma_commit(empty0 + 8 * s);
         }
-        if (ok) mma_commit(tfull0 + 8 * acc);
+        if (ok) {
+          if (CTAS == 2) mma_commit_pair(tfull0 + 8 * acc); else mma_commit(tfull0 + 8 * acc);
+        }
       }
     }
   } else {
@@ -180,9 +212,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t tcount = 0;
     bool failed = false;
     T* out = static_cast<T*>(p.out);
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+    const uint32_t tempty_even = CTAS == 2 ? mapa_shared(tempty0, 0) : 0u;
+    for (int tile = worker; tile < num_tiles; tile += workers, ++tcount) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+      if (CTAS == 2) tm = tm * 2 + (int)crank;  // this CTA's 128 rows of the 256-row tile
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       // All four epilogue warps leave together if any of their waits ran out (a warp must never be
       // left alone at the named barrier below); the same barrier protects the reuse of colp.
@@ -308,7 +342,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (want_ssq && row_ok) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      if (lane == 0) {
+        if (CTAS == 2) mbar_arrive_cluster(tempty_even + 8 * acc); else mbar_arrive(tempty0 + 8 * acc);
+      }
     }
     bulk_wait_all();  // no bulk copy of this thread may outlive the kernel's shared memory
   }
@@ -316,9 +352,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // ------------------------------------------------------------------ common exit
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (CTAS == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -398,26 +435,61 @@ extern "C" int ksb_fp8_gemm_rowstats(const void* a, const float* a_scale, const 
   return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
 }
 
+// 0: every CTA on its own (cta_group::1); 1: CTA pairs (cta_group::2) for every epilogue that writes local rows.
+// The pair form is the default: same bits, 2 - 20 % less time at the 75 600-token shapes under the power cap.
+static int g_pair_mode = 1;
+
+extern "C" int ksb_gemm_pair_mode(int mode) {
+  const int previous = g_pair_mode;
+  if (mode == 0 || mode == 1) g_pair_mode = mode;
+  return previous;
+}
+
+template <typename T, int CTAS>
+static int launch_gemm_as(const gemm::Params& p, const CUtensorMap& ta, const CUtensorMap& tw, int grid, cudaStream_t st) {
+  auto kernel = gemm::fp8_gemm_kernel<T, CTAS>;
+  constexpr int smem = gemm::Cfg<CTAS>::SMEM_BYTES;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
+  if (CTAS == 1) {
+    kernel<<<grid, gemm::THREADS, smem, st>>>(ta, tw, p);
+    return check_launch("fp8 gemm");
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(gemm::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, ta, tw, p) != cudaSuccess) return fail(KSB_ERR_CUDA, "cluster launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  return check_launch("fp8 gemm (CTA pairs)");
+}
+
 static int launch_gemm(gemm::Params& p, const void* a, const void* w, int dtype, cudaStream_t st) {
   const int64_t M = p.M, N = p.N, K = p.K;
   p.fetch_ahead = K <= 8192 ? 1 : 0;
+  const bool pair = g_pair_mode == 1 && p.epilogue != KSB_EPI_SCATTER_HEADS && sm_count() >= 2;
   CUtensorMap ta, tw;
   if (int rc = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K, (uint64_t)M, (uint64_t)K, gemm::BK, gemm::BM)) return rc;
-  if (int rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, (uint64_t)K, (uint64_t)N, (uint64_t)K, gemm::BK, gemm::BN)) return rc;
+  if (int rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, (uint64_t)K, (uint64_t)N, (uint64_t)K, gemm::BK, pair ? gemm::BN / 2 : gemm::BN)) return rc;
   p.group_m = 64;
   while (p.group_m > 8 && (int64_t)p.group_m * gemm::BM * K > (32ll << 20)) p.group_m >>= 1;
   p.status = status_words();
   if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");
-  const int tiles = (int)((M + gemm::BM - 1) / gemm::BM) * (int)((N + gemm::BN - 1) / gemm::BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  if (dtype == KSB_BF16) {
-    if (cudaFuncSetAttribute(gemm::fp8_gemm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES) != cudaSuccess)
-      return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
-    gemm::fp8_gemm_kernel<__nv_bfloat16><<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(ta, tw, p);
-  } else {
-    if (cudaFuncSetAttribute(gemm::fp8_gemm_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES) != cudaSuccess)
-      return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
-    gemm::fp8_gemm_kernel<__half><<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(ta, tw, p);
+  const int tiles_n = (int)((N + gemm::BN - 1) / gemm::BN);
+  if (pair) {
+    p.group_m >>= 1;  // counted in 256-row tiles
+    const int tiles = (int)((M + 2 * gemm::BM - 1) / (2 * gemm::BM)) * tiles_n;
+    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 2>(p, ta, tw, 2 * pairs, st) : launch_gemm_as<__half, 2>(p, ta, tw, 2 * pairs, st);
   }
-  return check_launch("fp8 gemm");
+  const int tiles = (int)((M + gemm::BM - 1) / gemm::BM) * tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 1>(p, ta, tw, grid, st) : launch_gemm_as<__half, 1>(p, ta, tw, grid, st);
 }

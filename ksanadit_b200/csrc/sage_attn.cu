@@ -305,16 +305,15 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const float qsc = p.qs[w.h * p.nq + w.qt];
       float m_ref = -INFINITY, l = 0.f;
       // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
-      // (the two scales of a 128-key tile are adjacent and 8-byte aligned: one load)
-      const float2* ks2 = reinterpret_cast<const float2*>(p.ks + static_cast<int64_t>(w.h) * nk64);
       int e_next = entry_at(w, 0);
-      float2 ks_next = __ldg(ks2 + (e_next >> 2));
+      float ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)], ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
       for (int j = 0; j < w.n; ++j) {
         const int e = e_next;
-        const float sc0 = qsc * ks_next.x, sc1 = qsc * ks_next.y;
+        const float sc0 = qsc * ks0_next, sc1 = qsc * ks1_next;
         if (j + 1 < w.n) {
           e_next = entry_at(w, j + 1);
-          ks_next = __ldg(ks2 + (e_next >> 2));
+          ks0_next = p.ks[w.h * nk64 + 2 * (e_next >> 2)];
+          ks1_next = p.ks[w.h * nk64 + 2 * (e_next >> 2) + 1];
         }
         const int t = e >> 2, halves = e & 3;
         const int valid = min(BKV, p.Lk - t * BKV);
@@ -322,8 +321,10 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!mbar_wait_warp(s_full, g & 1, p.status, (KERNEL_ID << 16) | 9)) { ok = false; break; }
         tc_fence_after();
         uint32_t s[4][32];
-        tmem_ld64<0>(tmem_s + lane_sel, s);
-        tmem_ld64<1>(tmem_s + lane_sel + 64, s);
+        tmem_ld32(tmem_s + lane_sel + 0, s[0]);
+        tmem_ld32(tmem_s + lane_sel + 32, s[1]);
+        tmem_ld32(tmem_s + lane_sel + 64, s[2]);
+        tmem_ld32(tmem_s + lane_sel + 96, s[3]);
         tmem_wait_ld();
         // the scores are in registers: hand the accumulator back to the MMA issuer
         tc_fence_before();
@@ -458,7 +459,6 @@ extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, co
   } else {
     n_peers = 0;
   }
-  if (reinterpret_cast<uintptr_t>(ks) % 8 != 0) return fail(KSB_ERR_INVALID, "ks must be 8-byte aligned (the two scales of a 128-key tile are read as one pair)");
   if ((tile_offsets == nullptr) != (tile_entries == nullptr)) return fail(KSB_ERR_INVALID, "tile_offsets and tile_entries must both be given or both be NULL");
   if ((out && !aligned16(out)) || out_token_stride % 8 != 0 || out_head_stride % 8 != 0) return fail(KSB_ERR_INVALID, "out must be 16-byte aligned with strides multiple of 8 elements");
   const int64_t nq = (Lq + 127) / 128, nkv = (Lk + 127) / 128;

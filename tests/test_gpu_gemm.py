@@ -111,3 +111,32 @@ def test_gemm_linearity_at_full_width():
     assert max_abs_rel(b2, a * 2) <= 1e-2
     ref = (xq[:64].float() @ wq.float().t()) * sx[:64, None] * sw[None]
     assert max_abs_rel(a[:64], ref) <= GEMM_MAX_ABS_REL
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (300, 200, 80), (1000, 768, 512), (129, 520, 1040)])
+@pytest.mark.parametrize("epilogue", ["none", "gelu", "gate"])
+def test_cta_pair_form_gives_the_bits_of_the_single_cta_form(M, N, K, epilogue):
+    """tcgen05.mma.cta_group::2 (two CTAs of a cluster on one 256-row tile, each with its own half of the operands) and
+    cta_group::1 accumulate the same products in the same order: equal outputs, ragged edges included (a pair whose
+    second CTA has no rows at all, a W tile cut by N, a K tail)."""
+    from ksanadit_b200 import _lib, ops
+    lib = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    xq = (torch.randn(M, K, device="cuda", generator=g) * 50).clamp(-448, 448).to(torch.float8_e4m3fn)
+    wq = (torch.randn(N, K, device="cuda", generator=g) * 50).clamp(-448, 448).to(torch.float8_e4m3fn)
+    sx, sw = torch.rand(M, device="cuda", generator=g) + 0.5, (torch.rand(N, device="cuda", generator=g) + 0.5) * 5e-4
+    bias = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    epi = {"none": _lib.EPI_NONE, "gelu": _lib.EPI_GELU_TANH, "gate": _lib.EPI_GATE_RESIDUAL}[epilogue]
+    resid = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16) if epilogue == "gate" else None
+    gate = torch.randn(1, N, device="cuda", generator=g).to(torch.bfloat16) if epilogue == "gate" else None
+    before = lib.ksb_gemm_pair_mode(-1)
+    try:
+        outs = []
+        for mode in (0, 1):
+            lib.ksb_gemm_pair_mode(mode)
+            assert lib.ksb_gemm_pair_mode(-1) == mode
+            outs.append(ops.fp8_gemm(xq, sx, wq, sw, bias, epilogue=epi, resid=resid, gate=gate))
+            _lib.assert_device_ok()
+    finally:
+        lib.ksb_gemm_pair_mode(before)
+    assert torch.equal(outs[0], outs[1])
