@@ -190,8 +190,8 @@ int ksb_sage_quant_int8(const void* x, int dtype, int64_t L, int64_t H, int64_t 
 /* How ksb_fp8_gemm (and _rowstats) drive the tensor cores: 0 = every CTA computes 128 x 256 tiles on its own
  * (tcgen05.mma.cta_group::1); 1 = two CTAs of a cluster share 256 x 256 tiles (cta_group::2), each fetching its own half
  * of the operands (the default; both forms give the same bits).  Sets the mode when `mode` is 0 or 1, leaves it
- * otherwise (pass -1 to query); returns the mode that was in force before the call.  Process-wide;
- * ksb_fp8_gemm_qkv_scatter always uses the single-CTA form. */
+ * otherwise (pass -1 to query); returns the mode that was in force before the call.  Process-wide, for every GEMM
+ * entry point. */
 int ksb_gemm_pair_mode(int mode);
 
 /* The QKV projection with row statistics: ksb_fp8_gemm with KSB_EPI_NONE that also writes, for every 256-column

@@ -28,7 +28,7 @@ namespace gemm {
 constexpr int BM = 128, BN = 256, BK = 128;  // BK in bytes == e4m3 elements
 constexpr int UMMA_K = 32;
 constexpr int A_BYTES = BM * BK;
-constexpr int THREADS = 192;
+constexpr int threads_for(int epilogue_warps) { return 64 + 32 * epilogue_warps; }
 constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID = 1;
 // Output staging of the scatter epilogue: one 128-byte row piece per epilogue thread, rows 144 bytes apart (the
@@ -38,13 +38,19 @@ constexpr int SCATTER_COLS = 64, SCATTER_ROW_BYTES = SCATTER_COLS * 2 + 16, SCAT
 // tile with tcgen05.mma.cta_group::2 -- each holds its 128 rows of A and 128 of the 256 rows of the W tile, so a
 // stage is 32 KB instead of 48 KB per CTA (a third less operand traffic from L2 and into shared memory per flop)
 // and six stages fit where four did.
-template <int CTAS> struct Cfg {
+//
+// EW epilogue warps: 4 (one thread per accumulator row and all 256 columns; the scatter epilogue) or 8 (two threads per
+// row, 128 columns each: GELU and the gated residual cost 15 - 20 instructions per element, and with four warps the
+// epilogue of a tile took longer than the main loop of the next one at K = 5120).
+template <int CTAS, int EW> struct Cfg {
   static constexpr int B_ROWS = BN / CTAS;
   static constexpr int B_BYTES = B_ROWS * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = CTAS == 1 ? 4 : 6;
-  // dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params 3 x 256 f32][barriers][scatter staging]
-  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 3 * BN * 4 + 256 + SCATTER_BYTES;
+  static constexpr int THREADS = threads_for(EW);
+  static constexpr int COLP_BYTES = 3 * BN * 4 + 128 * 4;  // [sw | bias | gate] x BN, then one float per row (sums of squares of the upper column half)
+  // dynamic shared memory: [1024 align slack][STAGES x (A | B)][col params][barriers][scatter staging (4 warps only)]
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + COLP_BYTES + 256 + (EW == 4 ? SCATTER_BYTES : 0);
 };
 
 struct Params {
@@ -99,18 +105,21 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return __fdividef(x, 1.f + __expf(-2.f * u));
 }
 
-template <typename T, int CTAS>
-__global__ void __launch_bounds__(THREADS, 1)
+template <typename T, int CTAS, int EW>
+__global__ void __launch_bounds__(threads_for(EW), 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const Params p) {
-  constexpr int STAGES = Cfg<CTAS>::STAGES, STAGE_BYTES = Cfg<CTAS>::STAGE_BYTES;
+  using C = Cfg<CTAS, EW>;
+  constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, COLP_BYTES = C::COLP_BYTES;
+  static_assert(EW == 4 || EW == 8, "four or eight epilogue warps");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   float* colp = reinterpret_cast<float*>(gen + STAGES * STAGE_BYTES);  // [sw | bias | gate] x BN
-  const uint32_t bars = base + STAGES * STAGE_BYTES + 3 * BN * 4;
+  float* ssq_upper = colp + 3 * BN;                                   // [128] (eight epilogue warps only)
+  const uint32_t bars = base + STAGES * STAGE_BYTES + COLP_BYTES;
   const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
   const uint32_t tmem_slot = tempty0 + 16;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + STAGES * STAGE_BYTES + 3 * BN * 4 + 16 * STAGES + 32);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + STAGES * STAGE_BYTES + COLP_BYTES + 16 * STAGES + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // A pair walks the 256-row tiles together; CTA `crank` of the pair owns rows crank * 128 .. + 127 of each.
@@ -127,7 +136,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
-      mbar_init(tempty0 + 8 * a, 4 * CTAS);  // one arrival per epilogue warp (of both CTAs, at the even CTA)
+      mbar_init(tempty0 + 8 * a, EW * CTAS);  // one arrival per epilogue warp (of both CTAs, at the even CTA)
     }
     fence_barrier_init();
   }
@@ -165,7 +174,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const uint32_t full_even = mapa_shared(full0 + 8 * s, 0);
             if (crank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
             tma_load_2d_pair(sa, &tmap_a, full_even, k * BK, (tm * 2 + (int)crank) * BM);
-            tma_load_2d_pair(sa + A_BYTES, &tmap_w, full_even, k * BK, tn * BN + (int)crank * Cfg<CTAS>::B_ROWS);
+            tma_load_2d_pair(sa + A_BYTES, &tmap_w, full_even, k * BK, tn * BN + (int)crank * C::B_ROWS);
           } else {
             mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
             tma_load_2d(sa, &tmap_a, full0 + 8 * s, k * BK, tm * BM);
@@ -205,10 +214,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2 .. 2 + EW - 1)
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const int et = threadIdx.x - 64;
-    uint8_t* stage_row = gen + STAGES * STAGE_BYTES + 3 * BN * 4 + 256 + et * SCATTER_ROW_BYTES;
+    constexpr int ET = EW * 32;           // epilogue threads
+    constexpr int CW = BN / (EW / 4);     // columns per thread: all 256, or the lower / upper 128
+    const int cbeg = ((warp - 2) >> 2) * CW, cend = cbeg + CW;
+    uint8_t* stage_row = gen + STAGES * STAGE_BYTES + COLP_BYTES + 256 + (EW == 4 ? et : 0) * SCATTER_ROW_BYTES;
     uint32_t tcount = 0;
     bool failed = false;
     T* out = static_cast<T*>(p.out);
@@ -220,16 +232,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       // All four epilogue warps leave together if any of their waits ran out (a warp must never be
       // left alone at the named barrier below); the same barrier protects the reuse of colp.
-      if (named_bar_or(1, 128, failed)) break;
+      if (named_bar_or(1, ET, failed)) break;
       // stage the per-column parameters of this tile
-      for (int c = et; c < BN; c += 128) {
+      for (int c = et; c < BN; c += ET) {
         const int n = tn * BN + c;
         const bool in = n < p.N;
         colp[c] = in ? p.sw[n] : 0.f;
         colp[BN + c] = (in && p.bias) ? HalfOps<T>::to_f(static_cast<const T*>(p.bias)[n]) : 0.f;
         colp[2 * BN + c] = (in && p.gate && p.gate_rows == 1) ? HalfOps<T>::to_f(static_cast<const T*>(p.gate)[n]) : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
       if (!mbar_wait_warp(tfull0 + 8 * acc, aph, p.status, (KERNEL_ID << 16) | 4)) { failed = true; continue; }
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
@@ -239,7 +251,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       T* orow = out + static_cast<int64_t>(row) * p.ldo + tn * BN;
       const T* rrow = p.resid ? static_cast<const T*>(p.resid) + static_cast<int64_t>(row) * p.ldr + tn * BN : nullptr;
       const T* grow = (p.gate && p.gate_rows != 1) ? static_cast<const T*>(p.gate) + static_cast<int64_t>(row / p.rows_per_gate) * p.N + tn * BN : nullptr;
-      const bool scatter = p.epilogue == KSB_EPI_SCATTER_HEADS;
+      const bool scatter = EW == 4 && p.epilogue == KSB_EPI_SCATTER_HEADS;
       const bool want_ssq = p.tile_sumsq != nullptr && tn * BN < p.sumsq_cols;
       float ssq = 0.f;
       // The residual (and a per-row gate) are fetched one 32-column chunk ahead when the main loop is short
@@ -252,14 +264,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
         for (int v8 = 0; v8 < 4; ++v8) {
           const int cb = c0 + v8 * 8;
-          const bool in = gated && c0 < BN && tn * BN + cb < p.N;
+          const bool in = gated && c0 < cend && tn * BN + cb < p.N;
           rv_next[v8] = in ? *reinterpret_cast<const uint4*>(rrow + cb) : make_uint4(0, 0, 0, 0);
           gv_next[v8] = (in && grow) ? *reinterpret_cast<const uint4*>(grow + cb) : make_uint4(0, 0, 0, 0);
         }
       };
-      if (p.fetch_ahead) fetch(0);
+      if (p.fetch_ahead) fetch(cbeg);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = cbeg; c0 < cend; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(t_row + c0, r);
         uint4 rv_cur[4], gv_cur[4];
@@ -339,7 +351,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         }
       }
-      if (want_ssq && row_ok) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
+      if (EW == 8) {
+        if (want_ssq) {  // uniform over the tile: the two threads of a row add their halves (lower + upper)
+          if (cbeg != 0) ssq_upper[q * 32 + lane] = ssq;
+          asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
+          if (cbeg == 0 && row_ok) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq + ssq_upper[q * 32 + lane];
+        }
+      } else {
+        if (want_ssq && row_ok) p.tile_sumsq[static_cast<int64_t>(tn) * p.M + row] = ssq;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -435,7 +455,12 @@ extern "C" int ksb_fp8_gemm_rowstats(const void* a, const float* a_scale, const 
   return launch_gemm(p, a, w, dtype, static_cast<cudaStream_t>(stream));
 }
 
-// 0: every CTA on its own (cta_group::1); 1: CTA pairs (cta_group::2) for every epilogue that writes local rows.
+// epilogue warps of every launch that writes local rows (the scatter epilogue always has four)
+#ifndef KSB_GEMM_EPILOGUE_WARPS
+#define KSB_GEMM_EPILOGUE_WARPS 8
+#endif
+
+// 0: every CTA on its own (cta_group::1); 1: CTA pairs (cta_group::2).
 // The pair form is the default: same bits, 2 - 20 % less time at the 75 600-token shapes under the power cap.
 static int g_pair_mode = 1;
 
@@ -445,19 +470,20 @@ extern "C" int ksb_gemm_pair_mode(int mode) {
   return previous;
 }
 
-template <typename T, int CTAS>
+template <typename T, int CTAS, int EW>
 static int launch_gemm_as(const gemm::Params& p, const CUtensorMap& ta, const CUtensorMap& tw, int grid, cudaStream_t st) {
-  auto kernel = gemm::fp8_gemm_kernel<T, CTAS>;
-  constexpr int smem = gemm::Cfg<CTAS>::SMEM_BYTES;
+  auto kernel = gemm::fp8_gemm_kernel<T, CTAS, EW>;
+  constexpr int smem = gemm::Cfg<CTAS, EW>::SMEM_BYTES;
+  constexpr int threads = gemm::Cfg<CTAS, EW>::THREADS;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
   if (CTAS == 1) {
-    kernel<<<grid, gemm::THREADS, smem, st>>>(ta, tw, p);
+    kernel<<<grid, threads, smem, st>>>(ta, tw, p);
     return check_launch("fp8 gemm");
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(gemm::THREADS, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -474,7 +500,7 @@ static int launch_gemm_as(const gemm::Params& p, const CUtensorMap& ta, const CU
 static int launch_gemm(gemm::Params& p, const void* a, const void* w, int dtype, cudaStream_t st) {
   const int64_t M = p.M, N = p.N, K = p.K;
   p.fetch_ahead = K <= 8192 ? 1 : 0;
-  const bool pair = g_pair_mode == 1 && p.epilogue != KSB_EPI_SCATTER_HEADS && sm_count() >= 2;
+  const bool pair = g_pair_mode == 1 && sm_count() >= 2;
   CUtensorMap ta, tw;
   if (int rc = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K, (uint64_t)M, (uint64_t)K, gemm::BK, gemm::BM)) return rc;
   if (int rc = encode_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w, (uint64_t)K, (uint64_t)N, (uint64_t)K, gemm::BK, pair ? gemm::BN / 2 : gemm::BN)) return rc;
@@ -487,9 +513,13 @@ static int launch_gemm(gemm::Params& p, const void* a, const void* w, int dtype,
     p.group_m >>= 1;  // counted in 256-row tiles
     const int tiles = (int)((M + 2 * gemm::BM - 1) / (2 * gemm::BM)) * tiles_n;
     const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-    return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 2>(p, ta, tw, 2 * pairs, st) : launch_gemm_as<__half, 2>(p, ta, tw, 2 * pairs, st);
+    if (p.epilogue == KSB_EPI_SCATTER_HEADS)
+      return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 2, 4>(p, ta, tw, 2 * pairs, st) : launch_gemm_as<__half, 2, 4>(p, ta, tw, 2 * pairs, st);
+    return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 2, KSB_GEMM_EPILOGUE_WARPS>(p, ta, tw, 2 * pairs, st) : launch_gemm_as<__half, 2, KSB_GEMM_EPILOGUE_WARPS>(p, ta, tw, 2 * pairs, st);
   }
   const int tiles = (int)((M + gemm::BM - 1) / gemm::BM) * tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 1>(p, ta, tw, grid, st) : launch_gemm_as<__half, 1>(p, ta, tw, grid, st);
+  if (p.epilogue == KSB_EPI_SCATTER_HEADS)
+    return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 1, 4>(p, ta, tw, grid, st) : launch_gemm_as<__half, 1, 4>(p, ta, tw, grid, st);
+  return dtype == KSB_BF16 ? launch_gemm_as<__nv_bfloat16, 1, KSB_GEMM_EPILOGUE_WARPS>(p, ta, tw, grid, st) : launch_gemm_as<__half, 1, KSB_GEMM_EPILOGUE_WARPS>(p, ta, tw, grid, st);
 }
