@@ -260,6 +260,10 @@ int ksb_sage_quant_v_fp8_noalloc(const void* v, int dtype, int64_t L, int64_t H,
  * gather heads" exchange (ksana/models/wan/wan_model.py:143-146) fused into the output stage: output row l goes
  * to peer_out[l / rows_per_peer] at row l % rows_per_peer, with the same strides as `out` (the caller offsets each
  * peer pointer to this rank's head slot).  The peers must be synchronised before they read. */
+/* Which kernel dense calls of ksb_sage_attn (no tile lists, no q_order) use: 1 = two Q blocks of a head per CTA sharing
+ * every K / V tile (the default), 0 = one block per CTA (the kernel that also serves tile lists).  Same arithmetic.
+ * Sets the mode when `mode` is 0 or 1, leaves it otherwise (pass -1 to query); returns the previous mode. */
+int ksb_attn_dual_mode(int mode);
 int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vs,
                   int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets, const int32_t* tile_entries,
                   const int32_t* q_order, void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride,

@@ -49,6 +49,7 @@ SIGNATURES = {
                                          c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p]),
     "ksb_rowsumsq_to_rstd_scatter": (c_int, [c_void_p, c_int64, c_int64, c_float, c_void_p, c_int, c_int, c_void_p]),
     "ksb_gemm_pair_mode": (c_int, [c_int]),
+    "ksb_attn_dual_mode": (c_int, [c_int]),
     "ksb_fp8_gemm_rowstats": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int,
                                       c_int64, c_void_p, c_int64, c_void_p]),
     "ksb_rowsumsq_to_rstd": (c_int, [c_void_p, c_int64, c_int64, c_int, c_float, c_void_p, c_void_p]),
@@ -81,6 +82,14 @@ def load():
         fn = getattr(lib, name)  # AttributeError here = header and library out of step
         fn.restype = res
         fn.argtypes = args
+    # KSANA_B200_GEMM_PAIR=0 selects the single-CTA GEMM form for the whole process (default: CTA pairs)
+    mode = os.environ.get("KSANA_B200_GEMM_PAIR")
+    if mode in ("0", "1"):
+        lib.ksb_gemm_pair_mode(int(mode))
+    # KSANA_B200_ATTN_DUAL=0 keeps dense attention on the one-block-per-CTA kernel (default: two blocks per CTA)
+    mode = os.environ.get("KSANA_B200_ATTN_DUAL")
+    if mode in ("0", "1"):
+        lib.ksb_attn_dual_mode(int(mode))
     _lib = lib
     return lib
 

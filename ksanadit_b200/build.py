@@ -14,7 +14,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libksana_b200.so")
-SOURCES = ["capi.cu", "rowwise_quant.cu", "fp8_gemm.cu", "sage_prepass.cu", "sage_attn.cu", "elementwise.cu"]
+SOURCES = ["capi.cu", "rowwise_quant.cu", "fp8_gemm.cu", "sage_prepass.cu", "sage_attn.cu", "sage_attn_dual.cu", "elementwise.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false",
