@@ -35,7 +35,7 @@ W14 = dict(layers=40, dim=5120, ffn=13824, heads=40, grid=(21, 45, 80), text_len
 # figure comes from a separate one-pass profiler capture (dram__bytes_read.sum + dram__bytes_write.sum) of a launch
 # with 8 heads of this shape, divided by the head count (every head reads its own Q, K and V and writes its own
 # output rows, so the bytes per head do not depend on how many heads a launch has); `roofline.traffic_source` says so.
-ATTN_DRAM_BYTES_PER_HEAD = (321428736 + 136435968) / 8
+ATTN_DRAM_BYTES_PER_HEAD = (250394112 + 124946432) / 8
 ATTN_TRAFFIC_SOURCE = ("profiler capture of one 75600-token launch (DRAM read + write counters), scaled by the head count; "
                        "not measured in this run")
 METRIC = "wan14b_dit_step_tflops"
@@ -481,7 +481,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": x_host.numel() * 2 + e_host.numel() * 2 + c_host.numel() * 2,
                     "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": launches,
-            "roofline": {"kernel": "sage_attn_kernel (self-attention)", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
+            "roofline": {"kernel": "sage_attn_dual_kernel (self-attention, two Q blocks per CTA)", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
                          "unit": "TFLOP/s", "frac": (achieved / fp8_peak) if achieved else None,
                          "peak_sustained": fp8_sustained, "frac_of_sustained": (achieved / fp8_sustained) if achieved else None,
                          "traffic": ATTN_DRAM_BYTES_PER_HEAD * Hl if L == 75600 else None,

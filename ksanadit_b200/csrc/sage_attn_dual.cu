@@ -7,7 +7,7 @@
 // settles ~6 % lower.
 //
 // Warp roles (384 threads):
-//   warp 0        TMA producer: both Q blocks once per work item, then K and V^T tiles through 3-deep rings
+//   warp 0        TMA producer: both Q blocks once per work item, then K and V^T tiles through 4-deep rings
 //   warps 1, 2    MMA issuer of half 0 / half 1 (one thread each): S = Q.K^T of tile j+1 queued before P.V of tile j;
 //                 a ring stage is free when both issuers' MMAs on it have completed (barrier count 2)
 //   warp 3        idle (donates registers)
@@ -23,7 +23,10 @@ namespace ksb {
 namespace attn {
 namespace dual {
 
-constexpr int RST = 3;             // K and V ring depth
+#ifndef KSB_ATTN_DUAL_RING
+#define KSB_ATTN_DUAL_RING 4
+#endif
+constexpr int RST = KSB_ATTN_DUAL_RING;  // K and V ring depth
 constexpr int THREADS2 = 384;
 constexpr int TMEM_COLS2 = 512;
 constexpr int KERNEL_ID2 = 3;

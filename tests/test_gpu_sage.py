@@ -57,6 +57,30 @@ def test_dense_core_many_work_items_persistent_loop():
     assert cosine(out, ref) >= ATT_COS and max_abs_rel(out, ref) <= ATT_MAR
 
 
+@pytest.mark.parametrize("Lq,Lk,H", [(128, 128, 1), (256, 128, 1), (63, 65, 2), (300, 520, 3), (5137, 700, 10), (128 * 31, 128 * 9 + 40, 40)])
+def test_two_blocks_per_cta_kernel_equals_the_one_block_kernel(Lq, Lk, H):
+    """Dense calls run on the kernel that keeps two Q blocks of a head in one CTA (shared K / V tiles); with the
+    switch off they run on the one-block kernel that also serves tile lists.  Same arithmetic in the same order: equal
+    outputs, for an odd number of Q blocks (a pair with one live half), ragged lengths, more work items than CTAs."""
+    from ksanadit_b200 import _lib, ops
+    lib = _lib.load()
+    q, k, v = _qkv(Lq, Lk, H, seed=Lq + Lk + H)
+    pp = Sg.sage_prepass(q, k, v)
+    args = [pp[n].cuda() for n in ("q8", "qs", "k8", "ks", "vt8", "vs")]
+    before = lib.ksb_attn_dual_mode(-1)
+    try:
+        outs = []
+        for mode in (0, 1):
+            lib.ksb_attn_dual_mode(mode)
+            assert lib.ksb_attn_dual_mode(-1) == mode
+            outs.append(ops.sage_attn_core(*args, Lq, Lk, q.dtype))
+            _lib.assert_device_ok()
+    finally:
+        lib.ksb_attn_dual_mode(before)
+    assert torch.equal(outs[0], outs[1])
+    assert bool(torch.isfinite(outs[1].float()).all())
+
+
 def test_large_score_range_exercises_rescale():
     q, k, v = _qkv(256, 1024, 1, seed=11)
     k[512:] *= 4  # later tiles carry much larger scores: the lazy maximum must move
