@@ -269,6 +269,17 @@ int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* 
                   const int32_t* q_order, void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride,
                   void* const* peer_out, int n_peers, int64_t rows_per_peer, ksb_stream_t stream);
 
+/* ksb_sage_attn with the tile lists given per PAIR of Q blocks (2i, 2i+1), for the kernel that keeps both blocks in one
+ * CTA and fetches every K / V tile once for the two: pair_offsets int32 [ceil(Lq_pad/256) + 1], pair_entries int32
+ * [nnz], entry = kv_tile*16 + keep bits of block 2i (bit0: tokens 0-63 of the tile, bit1: tokens 64-127) + keep bits of
+ * block 2i+1 (bits 2-3), the union of the two blocks' lists in ascending kv_tile order; pair_order (optional, int32
+ * [ceil(Lq_pad/256)]) a permutation of the pairs.  Same results as ksb_sage_attn with the per-block lists the pairs
+ * were built from.  Everything else as ksb_sage_attn. */
+int ksb_sage_attn_pairs(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vs,
+                        int64_t H, int64_t Lq, int64_t Lk, const int32_t* pair_offsets, const int32_t* pair_entries,
+                        const int32_t* pair_order, void* out, int dtype, int64_t out_token_stride, int64_t out_head_stride,
+                        void* const* peer_out, int n_peers, int64_t rows_per_peer, ksb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

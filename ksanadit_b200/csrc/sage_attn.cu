@@ -363,11 +363,11 @@ extern "C" int ksb_attn_dual_mode(int mode) {
   return previous;
 }
 
-extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
-                             const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,
-                             const int32_t* tile_entries, const int32_t* q_order, void* out, int dtype,
-                             int64_t out_token_stride, int64_t out_head_stride, void* const* peer_out, int n_peers,
-                             int64_t rows_per_peer, ksb_stream_t stream) {
+static int attn_entry(bool pair_lists, const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                      const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,
+                      const int32_t* tile_entries, const int32_t* q_order, void* out, int dtype,
+                      int64_t out_token_stride, int64_t out_head_stride, void* const* peer_out, int n_peers,
+                      int64_t rows_per_peer, ksb_stream_t stream) {
   if (dtype != KSB_BF16 && dtype != KSB_FP16) return fail(KSB_ERR_INVALID, "dtype must be KSB_BF16 or KSB_FP16");
   if (H <= 0 || Lq <= 0 || Lk <= 0) return fail(KSB_ERR_INVALID, "bad shape H=%lld Lq=%lld Lk=%lld", (long long)H, (long long)Lq, (long long)Lk);
   if (!q8 || !qs || !k8 || !ks || !vt || !vs || (!out && !peer_out)) return fail(KSB_ERR_INVALID, "null pointer");
@@ -397,6 +397,11 @@ extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, co
   p.status = status_words();
   if (!p.status) return fail(KSB_ERR_CUDA, "status words unavailable");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pair_lists) {
+    if (!tile_offsets) return fail(KSB_ERR_INVALID, "ksb_sage_attn_pairs needs the per-pair tile lists");
+    const int rc = ksb_attn_launch_dual(tq, tk, tv, p, dtype, st);
+    return rc == KSB_ERR_UNSUPPORTED ? fail(KSB_ERR_UNSUPPORTED, "the two-block attention kernel cannot run in this build") : rc;
+  }
   if (g_dual_mode == 1 && !tile_offsets && !q_order) {
     const int rc = ksb_attn_launch_dual(tq, tk, tv, p, dtype, st);
     if (rc != KSB_ERR_UNSUPPORTED) return rc;
@@ -414,4 +419,22 @@ extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, co
     attn::sage_attn_kernel<__half><<<grid, attn::THREADS, attn::SMEM_BYTES, st>>>(tq, tk, tv, p);
   }
   return check_launch("sage attention");
+}
+
+extern "C" int ksb_sage_attn(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                             const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* tile_offsets,
+                             const int32_t* tile_entries, const int32_t* q_order, void* out, int dtype,
+                             int64_t out_token_stride, int64_t out_head_stride, void* const* peer_out, int n_peers,
+                             int64_t rows_per_peer, ksb_stream_t stream) {
+  return attn_entry(false, q8, qs, k8, ks, vt, vs, H, Lq, Lk, tile_offsets, tile_entries, q_order, out, dtype, out_token_stride,
+                    out_head_stride, peer_out, n_peers, rows_per_peer, stream);
+}
+
+extern "C" int ksb_sage_attn_pairs(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                                   const float* vs, int64_t H, int64_t Lq, int64_t Lk, const int32_t* pair_offsets,
+                                   const int32_t* pair_entries, const int32_t* pair_order, void* out, int dtype,
+                                   int64_t out_token_stride, int64_t out_head_stride, void* const* peer_out, int n_peers,
+                                   int64_t rows_per_peer, ksb_stream_t stream) {
+  return attn_entry(true, q8, qs, k8, ks, vt, vs, H, Lq, Lk, pair_offsets, pair_entries, pair_order, out, dtype, out_token_stride,
+                    out_head_stride, peer_out, n_peers, rows_per_peer, stream);
 }

@@ -15,7 +15,12 @@
 // Tensor memory (512 columns): half h has S at 256 h, O at 256 h + 128.  The halves are independent pipelines; only
 // the producer and the ring barriers are shared, so one half's softmax still overlaps the other half's MMAs.
 // An odd last block pair has one live half; the other half's issuer keeps the rings moving by arriving in place of
-// its MMAs.  Tile lists (block-sparse masks) stay with the one-block kernel: two blocks rarely share a list.
+// its MMAs.
+// Tile lists (block-sparse masks) are given per PAIR of Q blocks: the union of the two blocks' lists, each entry =
+// KV tile * 16 + keep bits of block 2i (bits 0-1: tokens 0-63 / 64-127 of the tile) + keep bits of block 2i+1 (bits
+// 2-3).  Both halves walk the whole union; a half masks the 64-token halves it does not keep (a tile it does not keep
+// at all costs it a fully masked pass: P = 0), so pairing pays only where the two lists nearly coincide; the host
+// side decides (ops.py) and otherwise sends tile lists to the one-block kernel.
 #include "sage_attn_common.cuh"
 #include "host_utils.h"
 
@@ -35,6 +40,27 @@ constexpr int NUM_BARS2 = 32;
 constexpr int NUM_TILES2 = 2 + 4 + 2 * RST;
 constexpr int SMEM_BYTES2 = 1024 + NUM_TILES2 * TILE_BYTES + CONST_BYTES + 8 * NUM_BARS2 + 64;
 constexpr int PRODUCER_REGS = 56, SOFTMAX_REGS = 200;
+
+struct PairWork {
+  int h, pr, n;
+  const int32_t* ents;
+};
+__device__ __forceinline__ PairWork get_pair(const Params& p, int idx, int npairs) {
+  PairWork w;
+  w.h = idx / npairs;
+  w.pr = idx - w.h * npairs;
+  if (p.order) w.pr = p.order[w.pr];
+  if (p.offsets) {
+    const int a = p.offsets[w.pr];
+    w.n = p.offsets[w.pr + 1] - a;
+    w.ents = p.entries + a;
+  } else {
+    w.n = p.nkv;
+    w.ents = nullptr;
+  }
+  return w;
+}
+__device__ __forceinline__ int pair_entry(const PairWork& w, int j) { return w.ents ? w.ents[j] : (j * 16 + 15); }
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS2, 1)
@@ -103,20 +129,23 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       uint32_t wi = 0, it = 0;
       bool ok = true;
       for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
-        const int h = idx / npairs, qt0 = (idx - h * npairs) * 2;
+        const PairWork w = get_pair(p, idx, npairs);
+        if (w.n == 0) continue;
+        const int h = w.h, qt0 = w.pr * 2;
         const bool two = qt0 + 1 < p.nq;
         if (!mbar_wait(q_empty, (wi & 1) ^ 1, p.status, (KERNEL_ID2 << 16) | 1)) { ok = false; break; }
         mbar_arrive_expect_tx(q_full, (two ? 2 : 1) * TILE_BYTES);
         tma_load_2d(q_smem, &tmap_q, q_full, 0, (h * p.nq + qt0) * BQ);
         if (two) tma_load_2d(q_smem + TILE_BYTES, &tmap_q, q_full, 0, (h * p.nq + qt0 + 1) * BQ);
-        for (int j = 0; j < p.nkv; ++j, ++it) {
+        for (int j = 0; j < w.n; ++j, ++it) {
+          const int t = pair_entry(w, j) >> 4;
           const uint32_t s = it % RST, ph = (it / RST) & 1;
           if (!mbar_wait(k_empty + 8 * s, ph ^ 1, p.status, (KERNEL_ID2 << 16) | 2)) { ok = false; break; }
           mbar_arrive_expect_tx(k_full + 8 * s, TILE_BYTES);
-          tma_load_2d(k_smem + s * TILE_BYTES, &tmap_k, k_full + 8 * s, 0, (h * p.nkv + j) * BKV);
+          tma_load_2d(k_smem + s * TILE_BYTES, &tmap_k, k_full + 8 * s, 0, (h * p.nkv + t) * BKV);
           if (!mbar_wait(v_empty + 8 * s, ph ^ 1, p.status, (KERNEL_ID2 << 16) | 3)) { ok = false; break; }
           mbar_arrive_expect_tx(v_full + 8 * s, TILE_BYTES);
-          tma_load_2d(v_smem + s * TILE_BYTES, &tmap_v, v_full + 8 * s, j * BKV, h * D);
+          tma_load_2d(v_smem + s * TILE_BYTES, &tmap_v, v_full + 8 * s, t * BKV, h * D);
         }
         ++wi;
       }
@@ -149,12 +178,14 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         return true;
       };
       for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
-        const int h = idx / npairs, qt = (idx - h * npairs) * 2 + hf;
+        const PairWork w = get_pair(p, idx, npairs);
+        if (w.n == 0) continue;
+        const int nt = w.n, qt = w.pr * 2 + hf;
         if (!mbar_wait(q_full, wi & 1, p.status, (KERNEL_ID2 << 16) | 6)) { ok = false; break; }
         if (qt >= p.nq) {
           // no block for this half: hand every stage back as soon as it has been filled
           mbar_arrive(q_empty);
-          for (int j = 0; j < p.nkv && ok; ++j, ++itk, ++itv) {
+          for (int j = 0; j < nt && ok; ++j, ++itk, ++itv) {
             const uint32_t s = itk % RST, ph = (itk / RST) & 1;
             if (!mbar_wait(k_full + 8 * s, ph, p.status, (KERNEL_ID2 << 16) | 4)) { ok = false; break; }
             mbar_arrive(k_empty + 8 * s);
@@ -165,8 +196,8 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           continue;
         }
         if (!issue_qk(g)) { ok = false; break; }
-        for (int j = 0; j < p.nkv; ++j) {
-          if (j + 1 < p.nkv) {
+        for (int j = 0; j < nt; ++j) {
+          if (j + 1 < nt) {
             if (!issue_qk(g + 1)) { ok = false; break; }
           } else {
             mma_commit(q_empty);  // every S = Q.K^T of this block has been issued
@@ -208,7 +239,8 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     __syncwarp();
     if (lane == 0) mbar_arrive(s_empty);
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
-      const int h = idx / npairs, qt = (idx - h * npairs) * 2 + hf;
+      const PairWork w = get_pair(p, idx, npairs);
+      const int h = w.h, qt = w.pr * 2 + hf;
       if (qt >= p.nq) continue;
       const int qrow = qt * BQ + row;
       T* orow;
@@ -218,16 +250,29 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       } else {
         orow = out + static_cast<int64_t>(qrow) * p.out_ts + static_cast<int64_t>(h) * p.out_hs;
       }
+      if (w.n == 0) {  // both blocks of the pair have empty lists: zeros
+        if (qrow < p.Lq) {
+#pragma unroll
+          for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
       const float qsc = p.qs[h * p.nq + qt];
       float m_ref = -INFINITY, l = 0.f;
-      float ks0_next = p.ks[h * nk64], ks1_next = p.ks[h * nk64 + 1];
-      for (int j = 0; j < p.nkv; ++j) {
+      // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
+      int e_next = pair_entry(w, 0);
+      float ks0_next = p.ks[h * nk64 + 2 * (e_next >> 4)], ks1_next = p.ks[h * nk64 + 2 * (e_next >> 4) + 1];
+      for (int j = 0; j < w.n; ++j) {
+        const int e = e_next;
         const float sc0 = qsc * ks0_next, sc1 = qsc * ks1_next;
-        if (j + 1 < p.nkv) {
-          ks0_next = p.ks[h * nk64 + 2 * (j + 1)];
-          ks1_next = p.ks[h * nk64 + 2 * (j + 1) + 1];
+        if (j + 1 < w.n) {
+          e_next = pair_entry(w, j + 1);
+          ks0_next = p.ks[h * nk64 + 2 * (e_next >> 4)];
+          ks1_next = p.ks[h * nk64 + 2 * (e_next >> 4) + 1];
         }
-        const int valid = min(BKV, p.Lk - j * BKV);
+        const int t = e >> 4, halves = (e >> (2 * hf)) & 3;
+        const int valid = min(BKV, p.Lk - t * BKV);
+        const bool full = (halves == 3) && (valid == BKV);
         if (!mbar_wait_warp(s_full, g & 1, p.status, (KERNEL_ID2 << 16) | 9)) { ok = false; break; }
         tc_fence_after();
         uint32_t s[4][32];
@@ -240,13 +285,16 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_empty);
-        if (valid < BKV) {
-          // columns of the ragged last tile become -inf: never the maximum, P = 0
+        if (!full) {
+          // masked columns (ragged tail or a 64-token half this block does not keep) become -inf: never the maximum, P = 0
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i >= valid) s[c][i] = 0xff800000u;
+            for (int i = 0; i < 32; ++i) {
+              const int col = c * 32 + i;
+              const bool keep = (col < valid) && ((halves >> (col >> 6)) & 1);
+              if (!keep) s[c][i] = 0xff800000u;
+            }
         }
         // exact: both operands of the subtraction are integers below 2^24
         const float m_tile = fmaxf((tree_max64(s[0], s[1]) - S_MAGIC) * sc0, (tree_max64(s[2], s[3]) - S_MAGIC) * sc1);

@@ -107,3 +107,29 @@ def longest_first_order(offsets: np.ndarray) -> np.ndarray:
     """Permutation of the Q blocks by decreasing list length (stable), for the kernel's ``q_order`` argument."""
     counts = np.diff(np.asarray(offsets, dtype=np.int64))
     return np.argsort(-counts, kind="stable").astype(np.int32)
+
+
+def pair_tile_lists(offsets: np.ndarray, entries: np.ndarray):
+    """Per-block lists (``compact_tile_lists``) -> per-pair lists for the kernel that keeps Q blocks 2i and 2i+1 in
+    one CTA: (pair_offsets int32 [ceil(nq/2)+1], pair_entries int32 [nnz]), the union of the two blocks' KV tiles in
+    ascending order, entry = kv_tile * 16 + keep bits of block 2i + (keep bits of block 2i+1 << 2)."""
+    offsets = np.asarray(offsets, dtype=np.int64)
+    entries = np.asarray(entries, dtype=np.int64)
+    nq = offsets.size - 1
+    npairs = (nq + 1) // 2
+    if entries.size == 0:
+        return np.zeros(npairs + 1, dtype=np.int32), np.zeros(0, dtype=np.int32)
+    block = np.repeat(np.arange(nq, dtype=np.int64), np.diff(offsets))  # Q block of every entry
+    tile, keep = entries >> 2, entries & 3
+    ntiles = int(tile.max()) + 1
+    key = (block >> 1) * ntiles + tile                      # (pair, kv tile)
+    bits = keep << (2 * (block & 1))
+    uniq, inv = np.unique(key, return_inverse=True)          # sorted: by pair, then by tile
+    merged = np.zeros(uniq.size, dtype=np.int64)
+    np.bitwise_or.at(merged, inv, bits)
+    pair = uniq // ntiles
+    counts = np.bincount(pair, minlength=npairs)
+    pair_offsets = np.zeros(npairs + 1, dtype=np.int32)
+    np.cumsum(counts, out=pair_offsets[1:])
+    pair_entries = ((uniq % ntiles) * 16 + merged).astype(np.int32)
+    return pair_offsets, pair_entries

@@ -101,6 +101,54 @@ def test_sparse_core_matches_oracle(sorted_order):
     assert cosine(out, ref) >= ATT_COS and max_abs_rel(out, ref) <= ATT_MAR
 
 
+@pytest.mark.parametrize("Lq,Lk,H,density", [(128 * 9 + 50, 128 * 9 + 50, 2, 0.5), (128 * 6, 128 * 11 + 3, 3, 0.25), (128 * 7 + 1, 128 * 4, 1, 0.8)])
+def test_pair_lists_on_the_two_block_kernel_equal_block_lists_on_the_one_block_kernel(Lq, Lk, H, density):
+    """Block-sparse calls: with the switch on, the per-block lists are merged per pair of Q blocks and both blocks walk
+    the union, masking what they do not keep; with it off every block walks its own list on the one-block kernel.
+    Random 64-token-granular masks in which adjacent blocks share little (many fully masked passes), a pair of empty
+    lists, a pair with one empty list, an odd number of Q blocks, a ragged last KV tile: equal outputs, and equal to
+    the oracle within the block tolerance."""
+    from ksanadit_b200 import _lib, ops
+    from ksanadit_b200 import radial_mask as PM
+    lib = _lib.load()
+    q, k, v = _qkv(Lq, Lk, H, seed=Lq + Lk)
+    nq, nk64 = (Lq + 127) // 128, (Lk + 63) // 64
+    m = np.random.RandomState(Lq).random_sample((nq, nk64)) < density
+    m[0, :] = True
+    if nq > 3:
+        m[2, :] = False      # a pair whose two lists are empty -> zeros
+        m[3, :] = False
+    if nq > 5:
+        m[4, :] = False      # a pair with one empty list
+    pp = Sg.sage_prepass(q, k, v)
+    o, e = PM.compact_tile_lists(m)
+    offs, ents = torch.from_numpy(o).cuda(), torch.from_numpy(e).cuda()
+    order = torch.from_numpy(PM.longest_first_order(o)).cuda()
+    args = [pp[n].cuda() for n in ("q8", "qs", "k8", "ks", "vt8", "vs")]
+    before = lib.ksb_attn_dual_mode(-1)
+    limit = ops.PAIR_LIST_MAX_OVERHEAD
+    ops.PAIR_LIST_MAX_OVERHEAD = 1e9   # pair whatever the unions cost (the default pairs only lists that nearly coincide)
+    ops._PAIR_LISTS.clear()
+    try:
+        outs = []
+        for mode, od in ((0, None), (1, None), (1, order)):
+            lib.ksb_attn_dual_mode(mode)
+            outs.append(ops.sage_attn_core(*args, Lq, Lk, q.dtype, offs, ents, tile_order=od))
+            _lib.assert_device_ok()
+    finally:
+        lib.ksb_attn_dual_mode(before)
+        ops.PAIR_LIST_MAX_OVERHEAD = limit
+        ops._PAIR_LISTS.clear()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    if nq > 3:
+        assert float(outs[1][2 * 128:4 * 128].abs().max()) == 0.0
+    mask_full = np.zeros((nq, 2 * ((Lk + 127) // 128)), dtype=bool)
+    mask_full[:, :nk64] = m
+    ref = Sg.sage_core(pp, Lq, Lk, torch.from_numpy(mask_full), out_dtype=torch.float32)
+    got = outs[1].cpu().float()
+    assert cosine(got, ref) >= ATT_COS and max_abs_rel(got, ref) <= ATT_MAR
+
+
 def test_full_attention_close_to_exact_sdpa():
     """End to end (GPU pre-passes + core) against exact attention, with the reference's own bound for its
     Sage backend (tests/ksana/attention_op_test.py:183-186: max < 1e-1, mean < 1e-2) on its shape."""
