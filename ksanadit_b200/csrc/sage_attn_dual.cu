@@ -45,12 +45,14 @@ struct PairWork {
   int h, pr, n;
   const int32_t* ents;
 };
+// LISTS = false is the dense kernel: every pair walks all KV tiles and the list code compiles away.
+template <bool LISTS>
 __device__ __forceinline__ PairWork get_pair(const Params& p, int idx, int npairs) {
   PairWork w;
   w.h = idx / npairs;
   w.pr = idx - w.h * npairs;
-  if (p.order) w.pr = p.order[w.pr];
-  if (p.offsets) {
+  if (LISTS && p.order) w.pr = p.order[w.pr];
+  if (LISTS && p.offsets) {
     const int a = p.offsets[w.pr];
     w.n = p.offsets[w.pr + 1] - a;
     w.ents = p.entries + a;
@@ -60,9 +62,10 @@ __device__ __forceinline__ PairWork get_pair(const Params& p, int idx, int npair
   }
   return w;
 }
-__device__ __forceinline__ int pair_entry(const PairWork& w, int j) { return w.ents ? w.ents[j] : (j * 16 + 15); }
+template <bool LISTS>
+__device__ __forceinline__ int pair_entry(const PairWork& w, int j) { return (LISTS && w.ents) ? w.ents[j] : (j * 16 + 15); }
 
-template <typename T>
+template <typename T, bool LISTS>
 __global__ void __launch_bounds__(THREADS2, 1)
 sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const Params p) {
@@ -129,7 +132,7 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       uint32_t wi = 0, it = 0;
       bool ok = true;
       for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
-        const PairWork w = get_pair(p, idx, npairs);
+        const PairWork w = get_pair<LISTS>(p, idx, npairs);
         if (w.n == 0) continue;
         const int h = w.h, qt0 = w.pr * 2;
         const bool two = qt0 + 1 < p.nq;
@@ -138,7 +141,7 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tma_load_2d(q_smem, &tmap_q, q_full, 0, (h * p.nq + qt0) * BQ);
         if (two) tma_load_2d(q_smem + TILE_BYTES, &tmap_q, q_full, 0, (h * p.nq + qt0 + 1) * BQ);
         for (int j = 0; j < w.n; ++j, ++it) {
-          const int t = pair_entry(w, j) >> 4;
+          const int t = pair_entry<LISTS>(w, j) >> 4;
           const uint32_t s = it % RST, ph = (it / RST) & 1;
           if (!mbar_wait(k_empty + 8 * s, ph ^ 1, p.status, (KERNEL_ID2 << 16) | 2)) { ok = false; break; }
           mbar_arrive_expect_tx(k_full + 8 * s, TILE_BYTES);
@@ -178,7 +181,7 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         return true;
       };
       for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
-        const PairWork w = get_pair(p, idx, npairs);
+        const PairWork w = get_pair<LISTS>(p, idx, npairs);
         if (w.n == 0) continue;
         const int nt = w.n, qt = w.pr * 2 + hf;
         if (!mbar_wait(q_full, wi & 1, p.status, (KERNEL_ID2 << 16) | 6)) { ok = false; break; }
@@ -239,7 +242,7 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     __syncwarp();
     if (lane == 0) mbar_arrive(s_empty);
     for (int idx = blockIdx.x; idx < total && ok; idx += gridDim.x) {
-      const PairWork w = get_pair(p, idx, npairs);
+      const PairWork w = get_pair<LISTS>(p, idx, npairs);
       const int h = w.h, qt = w.pr * 2 + hf;
       if (qt >= p.nq) continue;
       const int qrow = qt * BQ + row;
@@ -260,17 +263,17 @@ sage_attn_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const float qsc = p.qs[h * p.nq + qt];
       float m_ref = -INFINITY, l = 0.f;
       // per-tile metadata (list entry and the two K-block scales) is fetched one tile ahead
-      int e_next = pair_entry(w, 0);
+      int e_next = pair_entry<LISTS>(w, 0);
       float ks0_next = p.ks[h * nk64 + 2 * (e_next >> 4)], ks1_next = p.ks[h * nk64 + 2 * (e_next >> 4) + 1];
       for (int j = 0; j < w.n; ++j) {
         const int e = e_next;
         const float sc0 = qsc * ks0_next, sc1 = qsc * ks1_next;
         if (j + 1 < w.n) {
-          e_next = pair_entry(w, j + 1);
+          e_next = pair_entry<LISTS>(w, j + 1);
           ks0_next = p.ks[h * nk64 + 2 * (e_next >> 4)];
           ks1_next = p.ks[h * nk64 + 2 * (e_next >> 4) + 1];
         }
-        const int t = e >> 4, halves = (e >> (2 * hf)) & 3;
+        const int t = LISTS ? (e >> 4) : j, halves = LISTS ? ((e >> (2 * hf)) & 3) : 3;
         const int valid = min(BKV, p.Lk - t * BKV);
         const bool full = (halves == 3) && (valid == BKV);
         if (!mbar_wait_warp(s_full, g & 1, p.status, (KERNEL_ID2 << 16) | 9)) { ok = false; break; }
@@ -398,12 +401,15 @@ using namespace ksb;
 int ksb_attn_launch_dual(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const attn::Params& p, int dtype,
                          cudaStream_t st) {
   namespace d = attn::dual;
-  const void* fn = dtype == KSB_BF16 ? reinterpret_cast<const void*>(d::sage_attn_dual_kernel<__nv_bfloat16>)
-                                     : reinterpret_cast<const void*>(d::sage_attn_dual_kernel<__half>);
+  const bool lists = p.offsets != nullptr;
+  const void* fn = dtype == KSB_BF16 ? (lists ? reinterpret_cast<const void*>(d::sage_attn_dual_kernel<__nv_bfloat16, true>)
+                                             : reinterpret_cast<const void*>(d::sage_attn_dual_kernel<__nv_bfloat16, false>))
+                                     : (lists ? reinterpret_cast<const void*>(d::sage_attn_dual_kernel<__half, true>)
+                                             : reinterpret_cast<const void*>(d::sage_attn_dual_kernel<__half, false>));
   // setmaxnreg.inc blocks until the CTA's register pool (registers at launch x threads) holds what it asks for:
   // refuse a build whose launch-time register count cannot cover the targets
-  static int checked[2] = {0, 0};
-  int& ck = checked[dtype == KSB_BF16 ? 0 : 1];
+  static int checked[4] = {0, 0, 0, 0};
+  int& ck = checked[(dtype == KSB_BF16 ? 0 : 1) + (lists ? 2 : 0)];
   if (ck == 0) {
     cudaFuncAttributes fa{};
     if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return fail(KSB_ERR_CUDA, "cannot read the attention kernel's attributes");
@@ -414,7 +420,12 @@ int ksb_attn_launch_dual(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
     return fail(KSB_ERR_CUDA, "cannot raise dynamic shared memory limit");
   const int64_t total = (int64_t)p.H * ((p.nq + 1) / 2);
   const int grid = (int)(total < sm_count() ? total : sm_count());
-  if (dtype == KSB_BF16) d::sage_attn_dual_kernel<__nv_bfloat16><<<grid, d::THREADS2, d::SMEM_BYTES2, st>>>(tq, tk, tv, p);
-  else d::sage_attn_dual_kernel<__half><<<grid, d::THREADS2, d::SMEM_BYTES2, st>>>(tq, tk, tv, p);
+  if (dtype == KSB_BF16) {
+    if (lists) d::sage_attn_dual_kernel<__nv_bfloat16, true><<<grid, d::THREADS2, d::SMEM_BYTES2, st>>>(tq, tk, tv, p);
+    else d::sage_attn_dual_kernel<__nv_bfloat16, false><<<grid, d::THREADS2, d::SMEM_BYTES2, st>>>(tq, tk, tv, p);
+  } else {
+    if (lists) d::sage_attn_dual_kernel<__half, true><<<grid, d::THREADS2, d::SMEM_BYTES2, st>>>(tq, tk, tv, p);
+    else d::sage_attn_dual_kernel<__half, false><<<grid, d::THREADS2, d::SMEM_BYTES2, st>>>(tq, tk, tv, p);
+  }
   return check_launch("sage attention (two Q blocks per CTA)");
 }
