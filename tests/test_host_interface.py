@@ -305,3 +305,27 @@ print("adopt ok")
 """
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "adopt ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_pair_tile_lists_are_the_unions_of_the_block_lists():
+    """radial_mask.pair_tile_lists: per pair of Q blocks the union of the two lists in ascending tile order, each entry
+    carrying both blocks' keep bits; odd block counts (last pair = one block), empty lists, an all-empty mask."""
+    import numpy as np
+
+    from ksanadit_b200 import radial_mask as PM
+    rng = np.random.RandomState(0)
+    for nq, nk64, density in [(1, 2, 0.5), (3, 7, 0.4), (8, 16, 0.4), (5, 9, 0.1), (4, 6, 0.0)]:
+        m = rng.random_sample((nq, nk64)) < density
+        o, e = PM.compact_tile_lists(m)
+        po, pe = PM.pair_tile_lists(o, e)
+        assert po.dtype == np.int32 and pe.dtype == np.int32 and po.size == (nq + 1) // 2 + 1 and po[-1] == pe.size
+        for pr in range((nq + 1) // 2):
+            want = {}
+            for b in (0, 1):
+                q = 2 * pr + b
+                if q < nq:
+                    for ent in e[o[q]:o[q + 1]]:
+                        want[int(ent) >> 2] = want.get(int(ent) >> 2, 0) | ((int(ent) & 3) << (2 * b))
+            got = pe[po[pr]:po[pr + 1]]
+            assert [int(x) >> 4 for x in got] == sorted(want)
+            assert {int(x) >> 4: int(x) & 15 for x in got} == want
