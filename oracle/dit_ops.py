@@ -239,7 +239,7 @@ def wan_block_forward(p, x, e, context, grid, linear="fp8", attn="sage", eps=1e-
 
 
 def make_wan_block_params(dim, ffn, heads, seed=0, dtype=torch.bfloat16, std=0.02):
-    """Seeded random-init parameters in BASELINE config-1 style (weights ~N(0, 0.02))."""
+    """Seeded random-init parameters in the style of the benchmark's configuration 1 (weights ~N(0, 0.02))."""
     g = torch.Generator().manual_seed(seed)
 
     def W(n, k):
@@ -262,7 +262,7 @@ def make_wan_block_params(dim, ffn, heads, seed=0, dtype=torch.bfloat16, std=0.0
 
 
 def make_activations(L, dim, seed=0, dtype=torch.bfloat16, outlier_frac=0.01, outlier_mul=20.0):
-    """x ~ N(0,1) with 1% of channels scaled x20 (BASELINE configs 1/2)."""
+    """x ~ N(0,1) with 1% of channels scaled x20 (the benchmark's configurations 1 and 2)."""
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(L, dim, generator=g)
     n_out = max(1, int(round(dim * outlier_frac)))

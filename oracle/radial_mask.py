@@ -6,7 +6,7 @@ Two mask builders:
   ``MaskMap.query_log_mask`` + the expansion in ``RadialSageAttentionImpl``
   (ksana/operations/attention/backends/radial_sage_attn/attn_mask.py:20-145 and
   radial_sage_attn.py:138-160) and is pinned against them by the golden fixtures.
-* ``bernoulli_frame_mask`` is the mask BASELINE config 5 specifies for the 720p
+* ``bernoulli_frame_mask`` is the mask the benchmark's configuration 5 specifies for the 720p
   shape, which the reference itself cannot build (its constructor requires the
   latent H and W to be multiples of block_size/8, radial_sage_attn.py:126-127):
   same-frame tiles always kept, a cross-frame tile kept with probability
@@ -99,7 +99,7 @@ def expand_to_q128_k64(tile_mask, bs):
 
 
 def bernoulli_frame_mask(L, tokens_per_frame, seed=0, tile=128):
-    """BASELINE config-5 mask -> bool [ceil(L/128), ceil(L/128)] (128 x 128 tiles)."""
+    """The benchmark's configuration-5 mask -> bool [ceil(L/128), ceil(L/128)] (128 x 128 tiles)."""
     nt = (L + tile - 1) // tile
     frame = (np.arange(nt) * tile) // tokens_per_frame
     d = np.abs(frame[:, None] - frame[None, :])
