@@ -34,9 +34,12 @@ def _to_tiles(pattern: np.ndarray, row_off: int, col_off: int, bs: int) -> np.nd
     non-empty columns are more than one third dense."""
     tpf = pattern.shape[0]
     span = ((tpf - 1) // bs + 1) * bs
+    # the reference pads the pair to (offset + span) and shrinks whole tiles only (attn_mask.py:20-32,98-105): what
+    # spills past the last whole tile of the padded block is dropped, also when the frame does not end on a tile edge
     rows, cols = (row_off + span) // bs, (col_off + span) // bs
-    canvas = np.zeros((rows * bs, cols * bs), dtype=bool)
+    canvas = np.zeros((row_off + span, col_off + span), dtype=bool)
     canvas[row_off:row_off + tpf, col_off:col_off + tpf] = pattern
+    canvas = canvas[:rows * bs, :cols * bs]
     dens = canvas.reshape(rows, bs, cols, bs).sum(axis=1, dtype=np.int64).astype(np.float32) / np.float32(bs)
     nonzero = (dens > 0).sum(axis=-1).astype(np.float32)
     high = (dens > np.float32(1 / 3)).sum(axis=-1).astype(np.float32)

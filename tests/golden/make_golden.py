@@ -214,7 +214,8 @@ def main():
     am.tqdm = lambda it, **k: it
     masks = {}
     for (vt, nf, bs, decay, s) in [(8 * 16 * 16, 8, 128, 0.5, 8 * 256), (12 * 24 * 16, 12, 128, 0.2, 12 * 384 + 256),
-                                   (9 * 16 * 24, 9, 64, 0.5, 9 * 384), (21 * 1280, 21, 128, 0.02, 21 * 1280)]:
+                                   (9 * 16 * 24, 9, 64, 0.5, 9 * 384), (21 * 1280, 21, 128, 0.02, 21 * 1280),
+                                   (10 * 360, 10, 128, 0.5, 10 * 360 + 77)]:  # last: frames that do not end on tile edges
         mm = MaskMap(video_token_num=vt, num_frame=nf, block_size=bs, device="cpu")
         ref_m = mm.query_log_mask(s, "radial", block_size=bs, decay_factor=decay).numpy()
         or_m = R.radial_log_mask(s, vt, nf, bs, decay)
