@@ -47,7 +47,8 @@ typedef void* ksb_stream_t;
 int ksb_version(void);
 const char* ksb_last_error(void);
 /* Synchronises the device, returns the status words written by kernels whose bounded waits ran out
- * (code 0 = none; code 1 = a wait timed out, detail = kernel id << 16 | wait site) and clears them.
+ * (code 0 = none; code 1 = a wait timed out, detail = kernel id << 16 | wait site; kernel ids: 1 FP8 GEMM,
+ * 2 attention with one Q block per CTA, 3 attention with two, 15 the self-test) and clears them.
  * The words are sticky: from the moment a wait has run out, every later wait of every kernel on that GPU gives
  * up at once and leaves its outputs unwritten, until this call has read the words.  A caller that consumes
  * results should therefore check once per step, at a point where it synchronises anyway. */
