@@ -180,7 +180,16 @@ def run_qwen(a):
                 print(f"qwen-image step on {world} GPUs (Ulysses, NCCL), {tag}: {layers} blocks, {Li_all}+{Lt} tokens, {Li} image rows per rank: "
                       f"{tt.item():.2f} ms  {fl / tt.item() / 1e9:.1f} TFLOP/s", flush=True)
 
-        report("eager launches", timeit(step, a.iters, a.warmup))
+        report("eager launches, block after block", timeit(step, a.iters, a.warmup))
+        from .qwen_block import B200QwenDenoiseStep
+        drv = B200QwenDenoiseStep(blocks)
+
+        def driven():
+            with torch.no_grad():
+                return drv(img, txt, temb, img_grid=grid)[1]
+
+        same = bool((step().float() == driven().float()).all())
+        report(f"step driver (modulations ahead + text stream; equals the plain loop: {same})", timeit(driven, a.iters, a.warmup))
         dist.barrier()
         dist.destroy_process_group()
         return

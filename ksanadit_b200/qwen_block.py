@@ -172,8 +172,10 @@ class B200QwenBlock(torch.nn.Module):
         its index names (the kernels take one modulation row per token), the text stream uses row 0.
 
         ``mods``: this block's modulation rows [rows, 12 C] when the caller has computed them ahead (``B200QwenDenoiseStep``).
-        ``side_stream``: a CUDA stream for the text stream's kernels (one GPU only): its few-tile GEMMs and row passes
-        then fill the idle SMs at the ends of the image stream's launches instead of running alone."""
+        ``side_stream``: a CUDA stream for the text stream's kernels: its few-tile GEMMs and row passes then fill the
+        idle SMs at the ends of the image stream's launches instead of running alone (under sequence parallelism the
+        text stream is replicated and as large as a rank's share of the image stream; the collectives stay on the
+        caller's stream)."""
         if hidden_states.shape[0] != 1:
             raise _lib.KsanaB200Error("batch 1 only")
         if img_grid is None and image_rotary_emb is None:
@@ -213,7 +215,7 @@ class B200QwenBlock(torch.nn.Module):
         qkv = torch.empty(Lt + Li, 3 * C, dtype=self.dtype, device=img.device)
         a = self.attn
         main = torch.cuda.current_stream()
-        side = side_stream if (side_stream is not None and P == 1) else None
+        side = side_stream  # the text stream's own kernels only: every collective stays on the main stream
 
         def on_text_stream(fn, after):
             """Runs fn on the text stream once ``after`` (an event of the main stream) has passed; returns its result and
@@ -274,8 +276,8 @@ class B200QwenDenoiseStep(torch.nn.Module):
     * every block's modulation rows depend on the timestep embedding only, and computing them streams 12 C x C weights
       per block through a one-row GEMM: they are all launched at the start of the step on a stream of their own, so
       the weight streaming hides under the first blocks' tensor-core work;
-    * ``text_stream=True`` (one GPU): the text stream's kernels of every block run on a second stream beside the image
-      stream's (see ``B200QwenBlock.forward``).
+    * ``text_stream=True`` (used on one or two ranks): the text stream's kernels of every block run on a second stream
+      beside the image stream's (see ``B200QwenBlock.forward``).
 
     The caller's stream waits for both before this returns, and the step can be captured into a CUDA graph."""
 
@@ -309,7 +311,10 @@ class B200QwenDenoiseStep(torch.nn.Module):
                 ev = torch.cuda.Event()
                 ev.record(mod_stream)
                 events.append(ev)
-        side = txt_stream if (self.text_stream and distribute.get_world_size() == 1) else None
+        # with four or more ranks a rank's kernels are so short (862 - 1723 image rows) that the step is bound by the
+        # host's launch rate, and the extra events and stream switches cost more than the overlap gives
+        # (8 ranks: 68.4 against 65.3 ms; 2 ranks: 71.4 against 77.0 ms; 1 rank: 96.7 against 102.4 ms)
+        side = txt_stream if (self.text_stream and distribute.get_world_size() <= 2) else None
         for i, blk in enumerate(self.blocks):
             main.wait_event(events[i])
             txt, img = blk(img, txt, temb, image_rotary_emb=image_rotary_emb, img_grid=img_grid, modulate_index=modulate_index,
